@@ -1,0 +1,405 @@
+"""D-NPEFF NMF benchmark: iterations/s of the multiplicative-update loop and the
+HBM roofline of its dominant kernel, on synthetic D-PEFs of BASELINE config 2
+(n=20,000 examples, m=4,194,304 features, 32,768 stored values per row, r=128).
+
+    python bench.py --gpus N --steps K --warmup W            # this engine
+    python bench.py --impl reference --steps K --warmup W    # CPU baseline arm
+
+One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE).  At N > 1 the
+SAME matrix is column-sharded over the ranks (strong scaling) and the per-shard
+A*H^T and H*H^T partials are all-reduced with NCCL inside the engine.
+
+A "step" is one NMF iteration: W update then H update.  `value` is timed with
+the matrix resident in HBM; `e2e` is the same loop timed through the C ABI from
+pinned HOST buffers: upload + normalise + prune + shard + K iterations + W and H
+read back.  Prints ONE JSON line on rank 0.
+"""
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: n, m, k, r, alpha, sigma, seed   (BASELINE.json configs, 1-based)
+    1: dict(n=2048, m=65536, k=4096, r=32, alpha=1.1, sigma=1.0, seed=0),
+    2: dict(n=20000, m=4194304, k=32768, r=128, alpha=1.1, sigma=1.0, seed=1),
+    3: dict(n=50000, m=16777216, k=65536, r=256, alpha=1.1, sigma=1.0, seed=2),
+    5: dict(n=50000, m=8388608, k=65536, r=512, alpha=1.4, sigma=2.0, seed=4),
+}
+EPS = 1e-12
+METRIC = "dnpeff_nmf_iterations_per_s"
+UNIT = "iter/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
+# from the ncu capture summarised under profiles/ (None until one exists).
+NCU_TRAFFIC_BYTES = {}
+
+
+def workload_name(cfg_id, c):
+    return "config%d: n=%d m=%d k=%d r=%d zipf=%.1f sigma=%.0f seed=%d eps=%g" % (
+        cfg_id, c["n"], c["m"], c["k"], c["r"], c["alpha"], c["sigma"], c["seed"], EPS)
+
+
+def measured_peak_hbm():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU every 200 ms (NVML, read-only)."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            }
+            while not self._stop_evt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self._stop_evt.wait(0.2)
+        except Exception as ex:  # no NVML: report that instead of clocks
+            self.reasons.add("unsampled: %s" % type(ex).__name__)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+# ---------------------------------------------------------------------------
+def cpu_baseline(c, sample_rows, host_vals, host_idx, host_norms, col_div=1, threads=None):
+    """Times the CPU oracle on `sample_rows` rows of the workload and scales the
+    row-proportional parts to the full row count.  The feature-proportional dense
+    parts (H*H^T, (W^T W)*H + update) are timed on the first m/col_div features
+    and scaled by col_div.  Returns (iter/s, description, cores)."""
+    from oracle import oracle as O
+    if threads:
+        O.set_num_threads(threads)
+    cores = O.num_threads()
+    n, m, k, r = c["n"], c["m"], c["k"], c["r"]
+    ns = sample_rows
+    rowptr = np.arange(ns + 1, dtype=np.int64) * k
+    v = O.normalize_rows(np.ascontiguousarray(host_vals[:ns]).ravel(), rowptr, host_norms[:ns])
+    col = np.ascontiguousarray(host_idx[:ns]).ravel()
+    W = O.init_uniform(0, ns * r, 1, 0, 0.01).reshape(ns, r)
+    Ht = O.init_uniform(0, m * r, 1, 1, 0.01).reshape(m, r)
+    mc = max(1, m // col_div)
+    t = {}
+
+    def timed(name, fn):
+        t0 = time.perf_counter()
+        out = fn()
+        t[name] = time.perf_counter() - t0
+        return out
+
+    AH = timed("spmm_ah", lambda: O.spmm(v, col, rowptr, Ht, acc64=False))
+    HH = timed("gram_h", lambda: O.gram(Ht[:mc], acc64=False))
+    W1 = timed("mu_w", lambda: O.mu_update(W, AH, HH, EPS, acc64=False))
+    cv, cr, cp = O.csr_to_csc(v, col, rowptr, m)
+    WA = timed("spmm_wa", lambda: O.spmm(cv, cr, cp, W1, acc64=False))
+    # A^T*W costs a fixed walk over all m features (zero + write r floats each)
+    # plus a per-entry part; timing it on a matrix with no entries gives the walk.
+    timed("spmm_wa", lambda: O.spmm(cv, cr, cp, W1, acc64=False))  # second run, warm
+    ep = np.zeros(m + 1, dtype=np.int64)
+    timed("spmm_wa_empty", lambda: O.spmm(cv[:1], cr[:1], ep, W1, acc64=False))
+    WW = timed("gram_w", lambda: O.gram(W1, acc64=False))
+    timed("mu_h", lambda: O.mu_update(Ht[:mc], WA[:mc], WW, EPS, acc64=False))
+    scale = n / float(ns)
+    fixed = min(t["spmm_wa_empty"], t["spmm_wa"])
+    per_row = (t["spmm_wa"] - fixed) / ns
+    it = ((t["spmm_ah"] + t["mu_w"] + t["gram_w"]) * scale + fixed + per_row * n
+          + (t["gram_h"] + t["mu_h"]) * (m / float(mc)))
+    desc = ("first %d of %d rows, 1 iteration, fp32-accumulate oracle; sparse and W-side times "
+            "scaled by %d/%d (A^T*W as fixed + per-row part); H-side dense parts timed on %d of %d features and scaled; "
+            "parts(s)=%s" % (ns, n, n, ns, mc, m, {a: round(b, 3) for a, b in t.items()}))
+    return 1.0 / it, desc, cores
+
+
+def run_reference_arm(args, c, cfg_id):
+    """`--impl reference`: the reference has no CPU implementation of this path
+    (its engine is cuSPARSE/cuBLAS); the timed CPU arm is the oracle port with
+    all host threads.  Data comes from the numpy generator (no GPU is touched)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    ns = args.cpu_sample_rows
+    rng = np.random.default_rng(c["seed"])
+    n, m, k = c["n"], c["m"], c["k"]
+    # Zipf(alpha) columns by inverse-CDF draws; repeats inside a row are replaced
+    # by fresh draws (successive sampling), values g^2 * lognormal sorted descending.
+    p = (np.arange(m, dtype=np.float64) + 1.0) ** (-c["alpha"])
+    cdf = np.cumsum(p)
+    idx = np.empty((ns, k), dtype=np.int32)
+    vals = np.empty((ns, k), dtype=np.float32)
+    for i in range(ns):
+        got = np.zeros(0, dtype=np.int64)
+        while len(got) < k:
+            draw = np.searchsorted(cdf, rng.random(4 * k) * cdf[-1])
+            got = np.unique(np.concatenate([got, draw]))
+        keep = rng.permutation(got)[:k]
+        idx[i] = keep
+        vals[i] = np.sort(rng.standard_normal(k) ** 2 * rng.lognormal(0.0, c["sigma"]))[::-1]
+    norms = np.sqrt((vals.astype(np.float64) ** 2).sum(1)).astype(np.float32)
+    results = []
+    for _ in range(max(args.warmup, 0) + max(args.steps, 1)):
+        results.append(cpu_baseline(c, ns, vals, idx, norms, col_div=8))
+    timed = results[max(args.warmup, 0):]
+    value = float(np.mean([x[0] for x in timed]))
+    desc, cores = timed[-1][1], timed[-1][2]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / value,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload_name(cfg_id, c)},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
+    ap.add_argument("--cpu-sample-rows", type=int, default=256)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--scale-rows", type=float, default=1.0,
+                    help="shrink n (profiling captures on a small case); not a bench value")
+    args = ap.parse_args()
+    cfg_id = args.config
+    c = dict(CONFIGS[cfg_id])
+    if args.scale_rows != 1.0:
+        c["n"] = max(1, int(c["n"] * args.scale_rows))
+    if args.impl == "reference":
+        return run_reference_arm(args, c, cfg_id)
+
+    import torch
+    import torch.distributed as dist
+    from npeff_ref_b200 import MuNmf, MuNmfParams
+    from npeff_ref_b200._lib import lib, check
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torchrun --nproc-per-node %d"
+                         % (args.gpus, world, args.gpus))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    n, m, k, r = c["n"], c["m"], c["k"], c["r"]
+    warm = max(args.warmup, 3)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    # ---- synthetic D-PEF arrays, generated in HBM (every rank: the same matrix)
+    d_vals = torch.empty((n, k), dtype=torch.float32, device="cuda")
+    d_idx = torch.empty((n, k), dtype=torch.int32, device="cuda")
+    d_norms = torch.empty((n,), dtype=torch.float32, device="cuda")
+    t0 = time.perf_counter()
+    check(lib().dnpeff_synth_pef_device(n, m, k, c["alpha"], c["sigma"], c["seed"],
+                                        d_vals.data_ptr(), d_idx.data_ptr(), d_norms.data_ptr(),
+                                        stream))
+    t_gen = time.perf_counter() - t0
+
+    def make_engine():
+        return MuNmf(MuNmfParams(rank=r, eps=EPS, seed=c["seed"]), device=local_rank,
+                     shard_index=rank, n_shards=world, stream=stream)
+
+    def join(eng):
+        if world > 1:
+            box = [MuNmf.make_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            eng.init_comm(box[0])
+
+    def global_scale(eng):
+        # Uniform(0,1) * sqrt(mean(A)/r), mean over all n * m_kept entries
+        s = torch.tensor([eng.a_sum()], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(s)
+        return math.sqrt(float(s.item()) / (n * eng.shape[1]) / r)
+
+    eng = make_engine()
+    t0 = time.perf_counter()
+    eng.set_csr_device(n, m, d_vals.data_ptr(), d_idx.data_ptr(), 0, k, d_norms.data_ptr(), 1)
+    t_load = time.perf_counter() - t0
+    join(eng)
+    eng.set_init_scale(global_scale(eng))
+    eng.init_factors()
+    _, m_kept, c0, ms, nnz = eng.shape
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warm):
+        eng.step_w()
+        eng.step_h()
+    barrier()
+    loss_before = eng.compute_uncached_loss()
+
+    # ---- timed region: K iterations, matrix resident in HBM ---------------------
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    eng.enable_timing(True)
+    eng.get_timing()
+    launches0 = eng.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        eng.step_w()
+        eng.step_h()
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = eng.launch_count() - launches0
+    timing = eng.get_timing()
+    eng.enable_timing(False)
+    clocks = sampler.stop()
+    loss_after = eng.compute_uncached_loss()
+    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    value = 1000.0 / ms_per_step
+
+    # ---- roofline of the dominant kernel (this rank's shard) --------------------
+    spmm_bytes = 8.0 * nnz + 4.0 * r * ms + 4.0 * n * r
+    per_kernel = {name: (tot / cnt if cnt else None) for name, (tot, cnt) in timing.items()}
+    dom = max(("spmm_ah", "spmm_wa"), key=lambda kname: timing[kname][0])
+    peak, peak_kind = measured_peak_hbm()
+    achieved = spmm_bytes / (per_kernel[dom] * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": achieved / peak, "peak_kind": "of " + peak_kind,
+        "traffic": NCU_TRAFFIC_BYTES.get((cfg_id, world, dom)),
+        "algorithmic_bytes_per_launch": spmm_bytes,
+        "ms_per_launch": {a: (round(b, 4) if b is not None else None) for a, b in per_kernel.items()},
+        "note": "gather of r floats per stored entry goes through L2, so the SpMM is not HBM-bound for r >= 64",
+    }
+    eng.close()
+
+    # ---- e2e: host buffers -> loader -> K iterations -> W,H back, through the C ABI
+    e2e = None
+    if not args.no_e2e:
+        h_vals = torch.empty((n, k), dtype=torch.float32, pin_memory=True)
+        h_idx = torch.empty((n, k), dtype=torch.int32, pin_memory=True)
+        h_norms = torch.empty((n,), dtype=torch.float32, pin_memory=True)
+        h_vals.copy_(d_vals)
+        h_idx.copy_(d_idx)
+        h_norms.copy_(d_norms)
+        torch.cuda.synchronize()
+        del d_vals, d_idx
+        torch.cuda.empty_cache()
+        W_out = torch.empty((n, r), dtype=torch.float32, pin_memory=True)
+        H_out = torch.empty((r, ms), dtype=torch.float32, pin_memory=True)
+        eng2 = make_engine()
+        join(eng2)
+        barrier()
+        ev0.record()
+        check(lib().dnpeff_set_csr(eng2._h, n, m, k, None, h_vals.data_ptr(), h_idx.data_ptr(),
+                                   h_norms.data_ptr(), 1))
+        eng2.set_init_scale(global_scale(eng2))
+        eng2.init_factors()
+        for _ in range(args.steps):
+            eng2.step_w()
+            eng2.step_h()
+        check(lib().dnpeff_get_w(eng2._h, W_out.data_ptr()))
+        check(lib().dnpeff_get_h(eng2._h, H_out.data_ptr()))
+        ev1.record()
+        barrier()
+        te = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te.item())
+        h2d = h_vals.numel() * 4 + h_idx.numel() * 4 + h_norms.numel() * 4
+        d2h = W_out.numel() * 4 + H_out.numel() * 4
+        e2e = {"value": args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps,
+               "ms_total": e2e_ms,
+               "what": "dnpeff_set_csr from pinned host arrays (upload, normalise, prune, shard, CSC) "
+                       "+ init + K iterations + dnpeff_get_w/get_h into pinned host arrays"}
+        eng2.close()
+        host_sample = (h_vals.numpy(), h_idx.numpy(), h_norms.numpy())
+    else:
+        ns = args.cpu_sample_rows
+        host_sample = (d_vals[:ns].cpu().numpy(), d_idx[:ns].cpu().numpy(), d_norms[:ns].cpu().numpy())
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        v, desc, cores = cpu_baseline(c, min(args.cpu_sample_rows, n), *host_sample)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(cfg_id, c), "n_cols_kept": m_kept,
+                       "nnz_per_rank": nnz, "shard": "columns/%d" % world,
+                       "l2": "inputs larger than L2 (A %.1f GB, H %.2f GB per rank)" % (
+                           16.0 * nnz / 1e9, 4.0 * r * ms / 1e9),
+                       "setup_s": {"generate": round(t_gen, 2), "load_resident": round(t_load, 2)},
+                       "loss_before_timed": loss_before, "loss_after_timed": loss_after},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

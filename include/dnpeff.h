@@ -1,0 +1,180 @@
+/*
+ * dnpeff.h -- C ABI of the B200 D-NPEFF factorization engine.
+ *
+ * The reference (mmatena/npeff_ref, cc/cuda_d_npeff) has no FFI or plugin
+ * interface for this path: it is reached through the `run_nmf_on_pefs` process
+ * (mains/run_nmf_on_pefs.cu) and, in process, through the public members of
+ * MuNmf<IndT> (src/nmf/sparse/multi_mu_dense_factors_nmf1.h:81,152,207,222,242)
+ * plus three host preprocessing functions.  Each entry point below names the
+ * reference interface it replaces.
+ *
+ * Conventions
+ *   - every function returns DNPEFF_OK (0) or a negative dnpeff_status; the
+ *     message of the last failure on the calling thread is dnpeff_last_error();
+ *     nothing throws or aborts across this boundary (the reference terminates
+ *     on every error, src/cuda/cuda_statuses.h:15-38);
+ *   - one engine owns ONE column shard of A on ONE device; a multi-GPU job is
+ *     one engine per device (one process or thread each) joined by
+ *     dnpeff_comm_init; calls on one engine must be serialised by the caller;
+ *   - host buffers are caller-owned; device memory is engine-owned and is
+ *     released by dnpeff_destroy;
+ *   - W is [n_rows, rank] row-major, H is [rank, n_cols] row-major at this
+ *     boundary: the layouts of the output file (src/io/nmf_decomp_h5.h:38-89);
+ *   - values are fp32, column ids int32, row offsets int64.
+ *   - there is no CPU fallback: without a usable CUDA device every compute
+ *     entry point fails with DNPEFF_ERR_CUDA.
+ */
+#ifndef DNPEFF_H_
+#define DNPEFF_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DNPEFF_ABI_VERSION 1
+
+typedef enum {
+    DNPEFF_OK = 0,
+    DNPEFF_ERR_INVALID = -1,   /* bad argument, shape or call order */
+    DNPEFF_ERR_CUDA = -2,      /* CUDA runtime failure, or no device */
+    DNPEFF_ERR_NCCL = -3,      /* NCCL missing or failed */
+    DNPEFF_ERR_DATA = -4,      /* malformed matrix: index out of range, duplicate column in a row */
+    DNPEFF_ERR_UNSUPPORTED = -5,
+    DNPEFF_ERR_IO = -6         /* file could not be read or written */
+} dnpeff_status;
+
+typedef struct dnpeff_engine dnpeff_engine;
+
+/* MuNmfParams (src/nmf/sparse/multi_mu_dense_factors_device_contexts1.h:36-55)
+ * and the values run_nmf_on_pefs.cu:190-200 fills in. */
+typedef struct {
+    int32_t rank;       /* --nmf_n_components */
+    float eps;          /* added to the denominator; the executable hard-codes 1e-8f */
+    uint64_t seed;      /* the executable hard-codes 43190432042 */
+    float init_scale;   /* factors start as init_scale * U(0,1]; <= 0 means 1.0 (reference) */
+    int32_t shard_index; /* which column range of the kept columns this engine owns */
+    int32_t n_shards;    /* number of column ranges (== number of engines in the job) */
+} dnpeff_params;
+
+const char* dnpeff_last_error(void);
+int dnpeff_abi_version(void);
+
+/* Number of CUDA devices visible; replaces cudaGetDeviceCount at
+ * run_nmf_on_pefs.cu:126 / multi_mu_dense_factors_nmf1.h:84. */
+int dnpeff_device_count(int* count);
+
+/* DeviceContext ctor + initializeCuda (…device_contexts1.h:129-170,360-376).
+ * `stream` is a cudaStream_t the engine launches on, or NULL to create one. */
+int dnpeff_create(const dnpeff_params* params, int device, void* stream, dnpeff_engine** out);
+int dnpeff_destroy(dnpeff_engine* eng);
+
+/* ---- loader: normalize -> prune -> shard -> CSR + CSC on the device -------
+ * Replaces PefSparseFishers::normalizeFishers_inPlace (src/io/pef_fisher_h5.h:38-52),
+ * removeSmallestL0NormColumns_inPlace (src/util/sparse_util.h:79-159),
+ * splitColumnWise (src/util/matrix_util.h:24-69) and moveAToDeviceAsync
+ * (…device_contexts1.h:182-195).
+ *   vals, colind : nnz entries; row i owns [rowptr[i], rowptr[i+1]), or
+ *                  [i*k, (i+1)*k) when rowptr == NULL (the D-PEF file's
+ *                  implicit offsets, pef_fisher_h5.h:175-177)
+ *   norms        : n_rows row norms (data/dense_fisher_norms) or NULL to skip
+ *                  the normalisation
+ *   n_cols_full  : dense_fisher_size
+ * The *_device form takes device pointers (inputs already resident in HBM);
+ * the inputs are not modified and may be released after the call returns. */
+int dnpeff_set_csr(dnpeff_engine* eng, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
+                   const int64_t* rowptr, const float* vals, const int32_t* colind,
+                   const float* norms, int32_t min_values_per_parameter);
+int dnpeff_set_csr_device(dnpeff_engine* eng, int64_t n_rows, int64_t n_cols_full,
+                          int64_t k_per_row, const int64_t* d_rowptr, const float* d_vals,
+                          const int32_t* d_colind, const float* d_norms,
+                          int32_t min_values_per_parameter);
+
+/* Shapes after the loader ran.  n_cols_kept = columns surviving the pruning
+ * (over all shards); this engine owns kept columns [col_start, col_start+n_cols_shard)
+ * (getSizeOfSplit, src/util/matrix_util.h:10-20). */
+int dnpeff_get_shape(dnpeff_engine* eng, int64_t* n_rows, int64_t* n_cols_kept,
+                     int64_t* col_start, int64_t* n_cols_shard, int64_t* nnz_shard);
+/* newToOgIndex of removeSmallestL0NormColumns_inPlace: n_cols_kept original ids. */
+int dnpeff_get_new_to_og(dnpeff_engine* eng, int32_t* out);
+/* The shard's CSR as splitColumnWise leaves it (bit-exact partition check). */
+int dnpeff_export_shard_csr(dnpeff_engine* eng, int64_t* rowptr, int32_t* colind, float* vals);
+/* The shard's CSC (values, row ids, n_cols_shard+1 offsets), rows ascending in a column. */
+int dnpeff_export_shard_csc(dnpeff_engine* eng, int64_t* colptr, int32_t* rowind, float* vals);
+/* sum of squares of the shard's stored values (computeASqNorm, …device_contexts1.h:274-294). */
+int dnpeff_a_sq_norm(dnpeff_engine* eng, double* out);
+/* sum of the shard's stored values (for the Uniform*sqrt(mean(A)/r) initial scale). */
+int dnpeff_a_sum(dnpeff_engine* eng, double* out);
+
+/* ---- factors --------------------------------------------------------------
+ * initializeW / initializeH / broadcastInitializedW (…device_contexts1.h:197-233,
+ * multi_mu_dense_factors_nmf1.h:131-135,358-375).  W: [n_rows, rank] row-major
+ * or NULL; H: this shard's [rank, n_cols_shard] row-major or NULL.  NULL means
+ * "generate": init_scale * U(0,1] from a counter-based hash of (seed, global
+ * element index), identical on every shard layout and reproducible on a CPU. */
+int dnpeff_init_factors(dnpeff_engine* eng, const float* W, const float* H);
+int dnpeff_set_init_scale(dnpeff_engine* eng, float init_scale);
+/* loadWToHostSync / loadHToHostSync + toRowMajor_inPlace
+ * (multi_mu_dense_factors_nmf1.h:207-240, src/util/matrices.h:49-62). */
+int dnpeff_get_w(dnpeff_engine* eng, float* out);
+int dnpeff_get_h(dnpeff_engine* eng, float* out);
+
+/* ---- multi-GPU ------------------------------------------------------------
+ * initializeNccl (multi_mu_dense_factors_nmf1.h:341-349).  The reference uses
+ * ncclCommInitAll in one process; here every engine joins with the 128-byte
+ * id made by dnpeff_nccl_unique_id on one of them. */
+int dnpeff_nccl_unique_id(void* id128);
+int dnpeff_comm_init(dnpeff_engine* eng, const void* id128, int comm_rank, int comm_size);
+
+/* ---- iteration ------------------------------------------------------------
+ * updateW / updateH / run (multi_mu_dense_factors_nmf1.h:152-205,293-339).
+ * dnpeff_run does `iters` x (step_w, step_h); when log_every > 0 it prints the
+ * reference's "step N: <loss> [<ms> ms/step]" line every log_every steps.
+ * All three are asynchronous on the engine's stream unless they log. */
+int dnpeff_step_w(dnpeff_engine* eng);
+int dnpeff_step_h(dnpeff_engine* eng);
+int dnpeff_run(dnpeff_engine* eng, int32_t iters, int32_t log_every);
+int dnpeff_synchronize(dnpeff_engine* eng);
+/* computeUncachedLoss (multi_mu_dense_factors_nmf1.h:242-274): the global
+ * sqrt(|A|^2 + <H,(W^T W)H> - 2<W^T A,H>), identical on every engine. */
+int dnpeff_loss(dnpeff_engine* eng, double* out);
+
+/* W-only fit with H fixed (Nmf::OnlyW::SparseH::Learner, src/nmf/sparse2/
+ * nmf_sparse_H.h:116-127,157-211,298-345): A*H^T and H*H^T once, then `iters`
+ * x  W *= AH / (W*HH + eps).  Uses the engine's current H; returns the loss
+ * sqrt(|A|^2 + <W*HH,W> - 2<AH,W>) when loss != NULL. */
+int dnpeff_fit_w_only(dnpeff_engine* eng, int32_t iters, double* loss);
+
+/* ---- measurement ----------------------------------------------------------
+ * Per-kernel device time (CUDA events on the engine's stream).  Kernel ids:
+ * 0 spmm A*H^T, 1 spmm A^T*W, 2 gram, 3 update, 4 allreduce, 5 loss. */
+#define DNPEFF_N_TIMERS 6
+int dnpeff_enable_timing(dnpeff_engine* eng, int enable);
+int dnpeff_get_timing(dnpeff_engine* eng, double ms_total[DNPEFF_N_TIMERS],
+                      int64_t launches[DNPEFF_N_TIMERS]);
+/* Number of kernel launches of this library since the engine was made. */
+int dnpeff_launch_count(dnpeff_engine* eng, int64_t* out);
+
+/* ---- single kernels on caller-owned device buffers ------------------------
+ * The building blocks above, exposed for kernel-level parity tests and
+ * benchmarks.  All pointers are device pointers; `stream` is a cudaStream_t.
+ *
+ * dnpeff_op_spmm: out[i,:] = sum_{p in [ptr[i],ptr[i+1])} vals[p] * D[ind[p],:],
+ *   out is [rows, r], D is [*, r], both row-major.  Replaces the two
+ *   cusparseSpMM calls (…device_contexts1.h:255-265; device_matrix_util.h:184-192).
+ * dnpeff_op_gram: G[r,r] = X^T X for X [rows, r].  Replaces the cublasSgemm
+ *   calls for H*H^T and W^T*W (…device_contexts1.h:303,322).
+ * dnpeff_op_mu_update: X[i,c] *= Num[i,c] / (sum_t X[i,t]*G[t,c] + eps).
+ *   Replaces cublasSgemm W*(HH^T) / (W^T W)*H (…device_contexts1.h:306,329)
+ *   fused with kernelNmfMuUpdate (src/nmf/sparse/kernels.h:24-34). */
+int dnpeff_op_spmm(const float* vals, const int32_t* ind, const int64_t* ptr, int64_t rows,
+                   const float* D, int32_t r, float* out, void* stream);
+int dnpeff_op_gram(const float* X, int64_t rows, int32_t r, float* G, void* stream);
+int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows, int32_t r,
+                        float eps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DNPEFF_H_ */

@@ -1,0 +1,911 @@
+// Host side of the D-NPEFF engine and its C ABI (see include/dnpeff.h).
+//
+// One engine = one column shard of the pruned PEF matrix A on one device:
+//   A  as CSR (rows = examples) and CSC (rows = features), fp32 + int32 + int64 offsets
+//   W  [n_rows, r] row-major, replicated on every engine of a job
+//   H  [n_cols_shard, r] row-major: the reference's column-major r x m_s matrix
+//      (multi_mu_dense_factors_device_contexts1.h:413-429), byte for byte
+// Iteration (multi_mu_dense_factors_nmf1.h:175-182): W first, then H.
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels_dense.cuh"
+#include "kernels_prep.cuh"
+#include "kernels_spmm.cuh"
+#include "nccl_dyn.h"
+
+using namespace dnpeff;
+
+namespace {
+
+template <typename T>
+struct DevBuf {
+    T* p = nullptr;
+    size_t count = 0;
+    DevBuf() {}
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+    ~DevBuf() { release(); }
+    int alloc(size_t n) {
+        release();
+        count = n;
+        DN_CUDA(cudaMalloc((void**)&p, sizeof(T) * (n ? n : 1)));
+        return DNPEFF_OK;
+    }
+    int alloc_zero(size_t n, cudaStream_t st) {
+        DN_TRY(alloc(n));
+        DN_CUDA(cudaMemsetAsync(p, 0, sizeof(T) * (n ? n : 1), st));
+        return DNPEFF_OK;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        count = 0;
+    }
+    T* take() {
+        T* q = p;
+        p = nullptr;
+        count = 0;
+        return q;
+    }
+};
+
+template <typename T>
+void dev_free(T*& p) {
+    if (p) cudaFree(p);
+    p = nullptr;
+}
+
+// Exclusive scan of N items into out[0..N) (int64).  Callers that want the
+// total pass N+1 items whose last one is zero.
+template <typename TIn>
+int scan_exclusive(const TIn* in, int64_t* out, int64_t N, cudaStream_t st) {
+    if (N <= 0) return DNPEFF_OK;
+    int64_t nb = ceil_div(N, 4096);
+    if (nb == 1) {
+        k_scan_block<TIn><<<1, 1024, 0, st>>>(in, out, nullptr, N);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+        return DNPEFF_OK;
+    }
+    DevBuf<int64_t> bs, bsp;
+    DN_TRY(bs.alloc((size_t)nb));
+    DN_TRY(bsp.alloc((size_t)nb));
+    k_scan_block<TIn><<<(unsigned)nb, 1024, 0, st>>>(in, out, bs.p, N);
+    DN_LAUNCH_CHECK();
+    DN_TRY(scan_exclusive<int64_t>(bs.p, bsp.p, nb, st));
+    k_scan_add<<<(unsigned)nb, 1024, 0, st>>>(out, bsp.p, N);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(2);
+    DN_CUDA(cudaStreamSynchronize(st));  // bs/bsp are released on return
+    return DNPEFF_OK;
+}
+
+struct TimedRegion {
+    int id;
+    cudaEvent_t a, b;
+};
+
+}  // namespace
+
+struct dnpeff_engine {
+    dnpeff_params p;
+    int device = 0;
+    cudaStream_t st = nullptr;
+    bool own_stream = false;
+
+    int64_t n = 0, m_full = 0, m_kept = 0, c0 = 0, ms = 0, nnz = 0;
+    bool loaded = false, have_factors = false, csc_ready = false;
+
+    float* a_vals = nullptr;
+    int32_t* a_col = nullptr;
+    int64_t* a_rowptr = nullptr;
+    float* c_vals = nullptr;
+    int32_t* c_row = nullptr;
+    int64_t* c_colptr = nullptr;
+    int32_t* new_to_og = nullptr;
+
+    float* W = nullptr;
+    float* H = nullptr;
+    float* AHG = nullptr;  // [n*r | r*r]: A*H^T partial and H*H^T partial, one allreduce
+    float* WA = nullptr;   // [ms*r], made on the first H update
+    float* WW = nullptr;   // [r*r]
+    float* gram_scratch = nullptr;
+    size_t gram_scratch_floats = 0;
+    double* red_partial = nullptr;  // device, 2*kRedBlocks doubles
+    double* red_out = nullptr;      // device, 4 doubles
+    SpmmPlan plan_csr, plan_csc;
+
+    double a_sq = 0.0, a_sum = 0.0;
+    double a_sq_global = -1.0;
+
+    ncclComm_t comm = nullptr;
+    int comm_rank = 0, comm_size = 1;
+
+    bool timing = false;
+    std::vector<TimedRegion> regions;
+    std::vector<cudaEvent_t> ev_pool;
+    double t_ms[DNPEFF_N_TIMERS] = {0};
+    int64_t t_n[DNPEFF_N_TIMERS] = {0};
+    int64_t launches0 = 0;
+};
+
+namespace {
+
+constexpr int kRedBlocks = 4 * kNumSMs;
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+struct ScopedTimer {
+    dnpeff_engine* e;
+    int id;
+    cudaEvent_t a = nullptr, b = nullptr;
+    ScopedTimer(dnpeff_engine* e_, int id_) : e(e_), id(id_) {
+        if (!e->timing) return;
+        a = get();
+        b = get();
+        cudaEventRecord(a, e->st);
+    }
+    ~ScopedTimer() {
+        if (!e->timing) return;
+        cudaEventRecord(b, e->st);
+        e->regions.push_back({id, a, b});
+    }
+    cudaEvent_t get() {
+        if (!e->ev_pool.empty()) {
+            cudaEvent_t x = e->ev_pool.back();
+            e->ev_pool.pop_back();
+            return x;
+        }
+        cudaEvent_t x;
+        cudaEventCreate(&x);
+        return x;
+    }
+};
+
+void free_matrix(dnpeff_engine* e) {
+    dev_free(e->a_vals); dev_free(e->a_col); dev_free(e->a_rowptr);
+    dev_free(e->c_vals); dev_free(e->c_row); dev_free(e->c_colptr);
+    dev_free(e->new_to_og);
+    dev_free(e->W); dev_free(e->H); dev_free(e->AHG); dev_free(e->WA); dev_free(e->WW);
+    dev_free(e->gram_scratch);
+    e->gram_scratch_floats = 0;
+    dev_free(e->plan_csr.long_list);
+    dev_free(e->plan_csc.long_list);
+    e->plan_csr = SpmmPlan();
+    e->plan_csc = SpmmPlan();
+    e->loaded = e->have_factors = e->csc_ready = false;
+    e->a_sq_global = -1.0;
+}
+
+int read_err_flag(int* d_err, cudaStream_t st, int* host) {
+    DN_CUDA(cudaMemcpyAsync(host, d_err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    DN_CUDA(cudaStreamSynchronize(st));
+    return DNPEFF_OK;
+}
+
+int data_error(int flags) {
+    if (flags & kErrColRange) return fail(DNPEFF_ERR_DATA, "column index outside [0, n_cols_full)");
+    if (flags & kErrRowPtr) return fail(DNPEFF_ERR_DATA, "row offsets are not non-decreasing");
+    if (flags & kErrDuplicate) return fail(DNPEFF_ERR_DATA, "a row holds the same column twice");
+    return DNPEFF_OK;
+}
+
+// getSizeOfSplit (src/util/matrix_util.h:10-20): equal widths, remainder to the last.
+void shard_range(int64_t total, int n_shards, int idx, int64_t* start, int64_t* size) {
+    int64_t base = total / n_shards;
+    *start = base * idx;
+    *size = (idx == n_shards - 1) ? base + total % n_shards : base;
+}
+
+int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const int64_t* d_rowptr,
+                const float* d_vals, const int32_t* d_col, const float* d_norms, int32_t min_count) {
+    if (n < 0 || m_full < 0 || (d_rowptr == nullptr && k < 0))
+        return fail(DNPEFF_ERR_INVALID, "negative shape");
+    if (n >= INT32_MAX || m_full >= INT32_MAX)
+        return fail(DNPEFF_ERR_UNSUPPORTED, "n_rows and n_cols_full must fit int32");
+    cudaStream_t st = e->st;
+    free_matrix(e);
+    const int r = e->p.rank;
+
+    int64_t nnz_in = n * k;
+    if (d_rowptr) {
+        if (n > 0) {
+            DN_CUDA(cudaMemcpyAsync(&nnz_in, d_rowptr + n, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+            DN_CUDA(cudaStreamSynchronize(st));
+        } else {
+            nnz_in = 0;
+        }
+    }
+    if (nnz_in < 0) return fail(DNPEFF_ERR_DATA, "negative nnz");
+
+    DevBuf<int> err;
+    DN_TRY(err.alloc_zero(1, st));
+    int herr = 0;
+
+    // 1. explicit entries per original column
+    DevBuf<int32_t> counts, flags, og_to_new;
+    DevBuf<int64_t> pos;
+    DN_TRY(counts.alloc_zero((size_t)m_full + 1, st));
+    if (nnz_in > 0) {
+        int64_t blocks = std::min<int64_t>(ceil_div(nnz_in, 256), (int64_t)kNumSMs * 16);
+        k_count_columns<<<(unsigned)blocks, 256, 0, st>>>(d_col, nnz_in, m_full, counts.p, err.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+    DN_TRY(read_err_flag(err.p, st, &herr));
+    if (herr) return data_error(herr);
+
+    // 2. keep mask -> ascending renumbering
+    DN_TRY(flags.alloc_zero((size_t)m_full + 1, st));
+    DN_TRY(pos.alloc((size_t)m_full + 1));
+    DN_TRY(og_to_new.alloc((size_t)m_full + 1));
+    if (m_full > 0) {
+        k_keep_flags<<<(unsigned)ceil_div(m_full, 256), 256, 0, st>>>(counts.p, m_full, min_count, flags.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+    DN_TRY(scan_exclusive<int32_t>(flags.p, pos.p, m_full + 1, st));
+    int64_t m_kept = 0;
+    DN_CUDA(cudaMemcpyAsync(&m_kept, pos.p + m_full, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    DN_CUDA(cudaStreamSynchronize(st));
+    DN_CUDA(cudaMalloc((void**)&e->new_to_og, sizeof(int32_t) * (size_t)std::max<int64_t>(m_kept, 1)));
+    if (m_full > 0) {
+        k_build_maps<<<(unsigned)ceil_div(m_full, 256), 256, 0, st>>>(flags.p, pos.p, m_full,
+                                                                     og_to_new.p, e->new_to_og);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+
+    // 3. this engine's range of kept columns
+    int64_t c0 = 0, ms = 0;
+    shard_range(m_kept, e->p.n_shards, e->p.shard_index, &c0, &ms);
+
+    // 4. shard row lengths -> row offsets
+    DevBuf<int32_t> row_count;
+    DN_TRY(row_count.alloc_zero((size_t)n + 1, st));
+    DN_CUDA(cudaMalloc((void**)&e->a_rowptr, sizeof(int64_t) * (size_t)(n + 1)));
+    if (n > 0) {
+        int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 32);
+        k_row_counts<<<(unsigned)blocks, 256, 0, st>>>(d_col, d_rowptr, k, n, og_to_new.p, c0, ms,
+                                                      row_count.p, err.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+    DN_TRY(scan_exclusive<int32_t>(row_count.p, e->a_rowptr, n + 1, st));
+    int64_t nnz = 0;
+    DN_CUDA(cudaMemcpyAsync(&nnz, e->a_rowptr + n, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    DN_TRY(read_err_flag(err.p, st, &herr));
+    if (herr) return data_error(herr);
+
+    // 5. order-preserving extraction with the row normalisation applied
+    DN_CUDA(cudaMalloc((void**)&e->a_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
+    DN_CUDA(cudaMalloc((void**)&e->a_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
+    if (n > 0) {
+        int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 32);
+        k_extract_shard<<<(unsigned)blocks, 256, 0, st>>>(d_vals, d_col, d_rowptr, k, n, d_norms,
+                                                         og_to_new.p, c0, ms, e->a_rowptr,
+                                                         e->a_vals, e->a_col);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+
+    // 6. column offsets of the shard's CSC (the arrays are filled on first use)
+    DevBuf<int32_t> cnt_s;
+    DN_TRY(cnt_s.alloc((size_t)ms + 1));
+    DN_CUDA(cudaMalloc((void**)&e->c_colptr, sizeof(int64_t) * (size_t)(ms + 1)));
+    k_gather_counts<<<(unsigned)ceil_div(ms + 1, 256), 256, 0, st>>>(counts.p, e->new_to_og, c0, ms, cnt_s.p);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(1);
+    DN_TRY(scan_exclusive<int32_t>(cnt_s.p, e->c_colptr, ms + 1, st));
+
+    // 7. |A|^2 and sum(A) of the shard
+    k_sum_sumsq<<<kRedBlocks, 256, 0, st>>>(e->a_vals, nnz, e->red_partial);
+    DN_LAUNCH_CHECK();
+    k_fold<<<1, 256, 0, st>>>(e->red_partial, kRedBlocks, 2, e->red_out);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(2);
+    double hs[2] = {0, 0};
+    DN_CUDA(cudaMemcpyAsync(hs, e->red_out, sizeof(double) * 2, cudaMemcpyDeviceToHost, st));
+    DN_CUDA(cudaStreamSynchronize(st));
+    e->a_sum = hs[0];
+    e->a_sq = hs[1];
+
+    e->n = n; e->m_full = m_full; e->m_kept = m_kept; e->c0 = c0; e->ms = ms; e->nnz = nnz;
+
+    // 8. factor and work buffers, long-row lists
+    DN_CUDA(cudaMalloc((void**)&e->W, sizeof(float) * (size_t)std::max<int64_t>(n * r, 1)));
+    DN_CUDA(cudaMalloc((void**)&e->H, sizeof(float) * (size_t)std::max<int64_t>(ms * r, 1)));
+    DN_CUDA(cudaMalloc((void**)&e->AHG, sizeof(float) * (size_t)(n * r + (int64_t)r * r)));
+    DN_CUDA(cudaMalloc((void**)&e->WW, sizeof(float) * (size_t)((int64_t)r * r)));
+    e->gram_scratch_floats = std::max(gram_plan(n, r).scratch_floats, gram_plan(ms, r).scratch_floats);
+    DN_CUDA(cudaMalloc((void**)&e->gram_scratch, sizeof(float) * e->gram_scratch_floats));
+    DN_TRY(spmm_make_plan(e->a_rowptr, n, &e->plan_csr, st));
+    DN_TRY(spmm_make_plan(e->c_colptr, ms, &e->plan_csc, st));
+    e->loaded = true;
+    return DNPEFF_OK;
+}
+
+// Stable CSC fill in waves of 64 rows (see kernels_prep.cuh).
+int build_csc(dnpeff_engine* e) {
+    if (e->csc_ready) return DNPEFF_OK;
+    cudaStream_t st = e->st;
+    DN_CUDA(cudaMalloc((void**)&e->c_vals, sizeof(float) * (size_t)std::max<int64_t>(e->nnz, 1)));
+    DN_CUDA(cudaMalloc((void**)&e->c_row, sizeof(int32_t) * (size_t)std::max<int64_t>(e->nnz, 1)));
+    if (e->nnz > 0) {
+        DevBuf<unsigned long long> mask, maxlen;
+        DevBuf<int32_t> cursor;
+        DevBuf<int> err;
+        DN_TRY(mask.alloc_zero((size_t)e->ms, st));
+        DN_TRY(cursor.alloc_zero((size_t)e->ms, st));
+        DN_TRY(maxlen.alloc_zero(1, st));
+        DN_TRY(err.alloc_zero(1, st));
+        k_max_rowlen<<<(unsigned)ceil_div(e->n, 256), 256, 0, st>>>(e->a_rowptr, e->n, maxlen.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+        unsigned long long hmax = 0;
+        DN_CUDA(cudaMemcpyAsync(&hmax, maxlen.p, sizeof(hmax), cudaMemcpyDeviceToHost, st));
+        DN_CUDA(cudaStreamSynchronize(st));
+        if (hmax > 0) {
+            dim3 grid((unsigned)ceil_div((int64_t)hmax, 256), 64);
+            for (int64_t base = 0; base < e->n; base += 64) {
+                k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->a_col, base, e->n, mask.p, err.p);
+                k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->a_col, e->a_vals, base, e->n, mask.p,
+                                                  e->c_colptr, cursor.p, e->c_vals, e->c_row);
+                k_csc_advance<<<grid, 256, 0, st>>>(e->a_rowptr, e->a_col, base, e->n, mask.p, cursor.p);
+                DN_COUNT_LAUNCH(3);
+            }
+            DN_LAUNCH_CHECK();
+        }
+        int herr = 0;
+        DN_TRY(read_err_flag(err.p, st, &herr));
+        if (herr) return data_error(herr);
+    }
+    e->csc_ready = true;
+    return DNPEFF_OK;
+}
+
+int allreduce_f32(dnpeff_engine* e, float* buf, size_t count) {
+    if (e->comm_size <= 1) return DNPEFF_OK;
+    ScopedTimer t(e, 4);
+    DN_NCCL(nccl_api().AllReduce(buf, buf, count, ncclFloat, ncclSum, e->comm, e->st));
+    return DNPEFF_OK;
+}
+
+int device_dot(dnpeff_engine* e, const float* a, const float* b, int64_t count, double* d_out) {
+    k_dot<<<kRedBlocks, 256, 0, e->st>>>(a, b, count, e->red_partial);
+    DN_LAUNCH_CHECK();
+    k_fold<<<1, 256, 0, e->st>>>(e->red_partial, kRedBlocks, 1, d_out);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(2);
+    return DNPEFF_OK;
+}
+
+int compute_ah_hh(dnpeff_engine* e) {
+    const int r = e->p.rank;
+    float* AH = e->AHG;
+    float* HH = e->AHG + e->n * r;
+    {
+        ScopedTimer t(e, 0);
+        DN_TRY(spmm_dispatch(e->a_vals, e->a_col, e->a_rowptr, e->n, e->H, r, AH, e->plan_csr, e->st));
+    }
+    {
+        ScopedTimer t(e, 2);
+        DN_TRY(gram_launch(e->H, e->ms, r, HH, e->gram_scratch, e->st));
+    }
+    DN_TRY(allreduce_f32(e, e->AHG, (size_t)(e->n * r + (int64_t)r * r)));
+    return DNPEFF_OK;
+}
+
+int step_w(dnpeff_engine* e) {
+    const int r = e->p.rank;
+    DN_TRY(compute_ah_hh(e));
+    ScopedTimer t(e, 3);
+    return mu_update_launch(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->st);
+}
+
+int step_h(dnpeff_engine* e) {
+    const int r = e->p.rank;
+    DN_TRY(build_csc(e));
+    if (!e->WA) DN_CUDA(cudaMalloc((void**)&e->WA, sizeof(float) * (size_t)std::max<int64_t>(e->ms * r, 1)));
+    {
+        ScopedTimer t(e, 1);
+        DN_TRY(spmm_dispatch(e->c_vals, e->c_row, e->c_colptr, e->ms, e->W, r, e->WA, e->plan_csc, e->st));
+    }
+    {
+        ScopedTimer t(e, 2);
+        DN_TRY(gram_launch(e->W, e->n, r, e->WW, e->gram_scratch, e->st));
+    }
+    ScopedTimer t(e, 3);
+    return mu_update_launch(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->st);
+}
+
+int global_a_sq(dnpeff_engine* e, double* out) {
+    if (e->a_sq_global < 0.0) {
+        if (e->comm_size > 1) {
+            DN_CUDA(cudaMemcpyAsync(e->red_out + 3, &e->a_sq, sizeof(double), cudaMemcpyHostToDevice, e->st));
+            DN_NCCL(nccl_api().AllReduce(e->red_out + 3, e->red_out + 3, 1, ncclDouble, ncclSum, e->comm, e->st));
+            double v = 0;
+            DN_CUDA(cudaMemcpyAsync(&v, e->red_out + 3, sizeof(double), cudaMemcpyDeviceToHost, e->st));
+            DN_CUDA(cudaStreamSynchronize(e->st));
+            e->a_sq_global = v;
+        } else {
+            e->a_sq_global = e->a_sq;
+        }
+    }
+    *out = e->a_sq_global;
+    return DNPEFF_OK;
+}
+
+// sqrt(|A|^2 + <W^T W, H H^T> - 2 <A H^T, W>).  <H,(W^T W)H> = <W^T W, H H^T> and
+// <W^T A, H> = <A H^T, W> are the reference's two Frobenius products
+// (…device_contexts1.h:337-354) written on the small side; after the allreduce
+// both are global, so every engine returns the same number.  The three terms
+// are accumulated in double.
+int loss_from_current(dnpeff_engine* e, bool recompute_ah, double* out) {
+    const int r = e->p.rank;
+    ScopedTimer t(e, 5);
+    if (recompute_ah) DN_TRY(compute_ah_hh(e));
+    DN_TRY(gram_launch(e->W, e->n, r, e->WW, e->gram_scratch, e->st));
+    DN_TRY(device_dot(e, e->AHG, e->W, e->n * r, e->red_out + 0));
+    DN_TRY(device_dot(e, e->WW, e->AHG + e->n * r, (int64_t)r * r, e->red_out + 1));
+    double h[2];
+    DN_CUDA(cudaMemcpyAsync(h, e->red_out, sizeof(double) * 2, cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    double a2 = 0;
+    DN_TRY(global_a_sq(e, &a2));
+    double sq = a2 + h[1] - 2.0 * h[0];
+    *out = sq > 0.0 ? sqrt(sq) : 0.0;
+    return DNPEFF_OK;
+}
+
+int init_generated(dnpeff_engine* e, bool do_w, bool do_h) {
+    const int r = e->p.rank;
+    float scale = e->p.init_scale > 0.f ? e->p.init_scale : 1.0f;
+    if (do_w && e->n > 0) {
+        k_init_uniform<<<kNumSMs * 8, 256, 0, e->st>>>(e->W, 0, e->n * r, stream_key(e->p.seed, 0), scale);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+    if (do_h && e->ms > 0) {
+        k_init_uniform<<<kNumSMs * 8, 256, 0, e->st>>>(e->H, e->c0 * r, e->ms * r,
+                                                     stream_key(e->p.seed, 1), scale);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+    return DNPEFF_OK;
+}
+
+int check_ready(dnpeff_engine* e, bool need_factors) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    if (!e->loaded) return fail(DNPEFF_ERR_INVALID, "no matrix loaded: call dnpeff_set_csr first");
+    if (need_factors && !e->have_factors)
+        return fail(DNPEFF_ERR_INVALID, "factors not initialised: call dnpeff_init_factors first");
+    return DNPEFF_OK;
+}
+
+// Scratch for the single-kernel entry points, one grow-only buffer per device.
+struct OpWorkspace {
+    std::mutex mu;
+    float* scratch[64] = {nullptr};
+    size_t floats[64] = {0};
+};
+OpWorkspace& op_ws() {
+    static OpWorkspace w;
+    return w;
+}
+
+int op_scratch(size_t floats, float** out) {
+    int dev = 0;
+    DN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(DNPEFF_ERR_UNSUPPORTED, "device ordinal %d", dev);
+    OpWorkspace& w = op_ws();
+    std::lock_guard<std::mutex> lk(w.mu);
+    if (w.floats[dev] < floats) {
+        if (w.scratch[dev]) {
+            DN_CUDA(cudaDeviceSynchronize());
+            cudaFree(w.scratch[dev]);
+            w.scratch[dev] = nullptr;
+            w.floats[dev] = 0;
+        }
+        DN_CUDA(cudaMalloc((void**)&w.scratch[dev], sizeof(float) * floats));
+        w.floats[dev] = floats;
+    }
+    *out = w.scratch[dev];
+    return DNPEFF_OK;
+}
+
+}  // namespace
+
+// ===========================================================================
+extern "C" {
+
+const char* dnpeff_last_error(void) { return err_buf(); }
+int dnpeff_abi_version(void) { return DNPEFF_ABI_VERSION; }
+
+int dnpeff_device_count(int* count) {
+    if (!count) return fail(DNPEFF_ERR_INVALID, "null argument");
+    *count = 0;
+    DN_CUDA(cudaGetDeviceCount(count));
+    return DNPEFF_OK;
+}
+
+int dnpeff_create(const dnpeff_params* params, int device, void* stream, dnpeff_engine** out) {
+    if (!params || !out) return fail(DNPEFF_ERR_INVALID, "null argument");
+    if (params->rank <= 0) return fail(DNPEFF_ERR_INVALID, "rank must be positive");
+    if (params->n_shards <= 0 || params->shard_index < 0 || params->shard_index >= params->n_shards)
+        return fail(DNPEFF_ERR_INVALID, "shard_index/n_shards out of range");
+    int ndev = 0;
+    DN_CUDA(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev)
+        return fail(DNPEFF_ERR_CUDA, "device %d not available (%d visible)", device, ndev);
+    DN_CUDA(cudaSetDevice(device));
+    dnpeff_engine* e = new dnpeff_engine();
+    e->p = *params;
+    e->device = device;
+    if (stream) {
+        e->st = (cudaStream_t)stream;
+    } else {
+        cudaError_t ce = cudaStreamCreateWithFlags(&e->st, cudaStreamNonBlocking);
+        if (ce != cudaSuccess) {
+            delete e;
+            return fail(DNPEFF_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(ce));
+        }
+        e->own_stream = true;
+    }
+    if (cudaMalloc((void**)&e->red_partial, sizeof(double) * 2 * kRedBlocks) != cudaSuccess ||
+        cudaMalloc((void**)&e->red_out, sizeof(double) * 4) != cudaSuccess) {
+        dnpeff_destroy(e);
+        return fail(DNPEFF_ERR_CUDA, "cudaMalloc of reduction buffers failed");
+    }
+    e->launches0 = launch_counter();
+    *out = e;
+    return DNPEFF_OK;
+}
+
+int dnpeff_destroy(dnpeff_engine* e) {
+    if (!e) return DNPEFF_OK;
+    DeviceGuard g(e->device);
+    cudaStreamSynchronize(e->st);
+    if (e->comm) nccl_api().CommDestroy(e->comm);
+    free_matrix(e);
+    dev_free(e->red_partial);
+    dev_free(e->red_out);
+    for (auto& r : e->regions) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    for (auto ev : e->ev_pool) cudaEventDestroy(ev);
+    if (e->own_stream) cudaStreamDestroy(e->st);
+    delete e;
+    return DNPEFF_OK;
+}
+
+int dnpeff_set_csr_device(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
+                          const int64_t* d_rowptr, const float* d_vals, const int32_t* d_colind,
+                          const float* d_norms, int32_t min_values_per_parameter) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    DeviceGuard g(e->device);
+    int s = load_device(e, n_rows, n_cols_full, k_per_row, d_rowptr, d_vals, d_colind, d_norms,
+                        min_values_per_parameter);
+    if (s != DNPEFF_OK) free_matrix(e);
+    return s;
+}
+
+int dnpeff_set_csr(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
+                   const int64_t* rowptr, const float* vals, const int32_t* colind,
+                   const float* norms, int32_t min_values_per_parameter) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    if (n_rows < 0) return fail(DNPEFF_ERR_INVALID, "negative shape");
+    DeviceGuard g(e->device);
+    int64_t nnz = rowptr ? (n_rows > 0 ? rowptr[n_rows] : 0) : n_rows * k_per_row;
+    if (nnz < 0) return fail(DNPEFF_ERR_DATA, "negative nnz");
+    if (nnz > 0 && (!vals || !colind)) return fail(DNPEFF_ERR_INVALID, "null vals/colind");
+    free_matrix(e);
+    DevBuf<float> dv, dn;
+    DevBuf<int32_t> dc;
+    DevBuf<int64_t> dr;
+    DN_TRY(dv.alloc((size_t)nnz));
+    DN_TRY(dc.alloc((size_t)nnz));
+    if (nnz > 0) {
+        DN_CUDA(cudaMemcpyAsync(dv.p, vals, sizeof(float) * (size_t)nnz, cudaMemcpyHostToDevice, e->st));
+        DN_CUDA(cudaMemcpyAsync(dc.p, colind, sizeof(int32_t) * (size_t)nnz, cudaMemcpyHostToDevice, e->st));
+    }
+    if (rowptr) {
+        DN_TRY(dr.alloc((size_t)n_rows + 1));
+        DN_CUDA(cudaMemcpyAsync(dr.p, rowptr, sizeof(int64_t) * (size_t)(n_rows + 1), cudaMemcpyHostToDevice, e->st));
+    }
+    if (norms) {
+        DN_TRY(dn.alloc((size_t)n_rows));
+        if (n_rows > 0)
+            DN_CUDA(cudaMemcpyAsync(dn.p, norms, sizeof(float) * (size_t)n_rows, cudaMemcpyHostToDevice, e->st));
+    }
+    int s = dnpeff_set_csr_device(e, n_rows, n_cols_full, k_per_row, rowptr ? dr.p : nullptr, dv.p,
+                                  dc.p, norms ? dn.p : nullptr, min_values_per_parameter);
+    cudaStreamSynchronize(e->st);
+    return s;
+}
+
+int dnpeff_get_shape(dnpeff_engine* e, int64_t* n_rows, int64_t* n_cols_kept, int64_t* col_start,
+                     int64_t* n_cols_shard, int64_t* nnz_shard) {
+    DN_TRY(check_ready(e, false));
+    if (n_rows) *n_rows = e->n;
+    if (n_cols_kept) *n_cols_kept = e->m_kept;
+    if (col_start) *col_start = e->c0;
+    if (n_cols_shard) *n_cols_shard = e->ms;
+    if (nnz_shard) *nnz_shard = e->nnz;
+    return DNPEFF_OK;
+}
+
+int dnpeff_get_new_to_og(dnpeff_engine* e, int32_t* out) {
+    DN_TRY(check_ready(e, false));
+    DeviceGuard g(e->device);
+    if (e->m_kept > 0) {
+        DN_CUDA(cudaMemcpyAsync(out, e->new_to_og, sizeof(int32_t) * (size_t)e->m_kept, cudaMemcpyDeviceToHost, e->st));
+        DN_CUDA(cudaStreamSynchronize(e->st));
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_export_shard_csr(dnpeff_engine* e, int64_t* rowptr, int32_t* colind, float* vals) {
+    DN_TRY(check_ready(e, false));
+    DeviceGuard g(e->device);
+    if (rowptr) DN_CUDA(cudaMemcpyAsync(rowptr, e->a_rowptr, sizeof(int64_t) * (size_t)(e->n + 1), cudaMemcpyDeviceToHost, e->st));
+    if (colind && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(colind, e->a_col, sizeof(int32_t) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+    if (vals && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(vals, e->a_vals, sizeof(float) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    return DNPEFF_OK;
+}
+
+int dnpeff_export_shard_csc(dnpeff_engine* e, int64_t* colptr, int32_t* rowind, float* vals) {
+    DN_TRY(check_ready(e, false));
+    DeviceGuard g(e->device);
+    DN_TRY(build_csc(e));
+    if (colptr) DN_CUDA(cudaMemcpyAsync(colptr, e->c_colptr, sizeof(int64_t) * (size_t)(e->ms + 1), cudaMemcpyDeviceToHost, e->st));
+    if (rowind && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(rowind, e->c_row, sizeof(int32_t) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+    if (vals && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(vals, e->c_vals, sizeof(float) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    return DNPEFF_OK;
+}
+
+int dnpeff_a_sq_norm(dnpeff_engine* e, double* out) {
+    DN_TRY(check_ready(e, false));
+    *out = e->a_sq;
+    return DNPEFF_OK;
+}
+
+int dnpeff_a_sum(dnpeff_engine* e, double* out) {
+    DN_TRY(check_ready(e, false));
+    *out = e->a_sum;
+    return DNPEFF_OK;
+}
+
+int dnpeff_set_init_scale(dnpeff_engine* e, float init_scale) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    e->p.init_scale = init_scale;
+    return DNPEFF_OK;
+}
+
+int dnpeff_init_factors(dnpeff_engine* e, const float* W, const float* H) {
+    DN_TRY(check_ready(e, false));
+    DeviceGuard g(e->device);
+    const int r = e->p.rank;
+    DN_TRY(init_generated(e, W == nullptr, H == nullptr));
+    if (W && e->n > 0)
+        DN_CUDA(cudaMemcpyAsync(e->W, W, sizeof(float) * (size_t)(e->n * r), cudaMemcpyHostToDevice, e->st));
+    if (H && e->ms > 0) {
+        DevBuf<float> tmp;
+        DN_TRY(tmp.alloc((size_t)(e->ms * r)));
+        DN_CUDA(cudaMemcpyAsync(tmp.p, H, sizeof(float) * (size_t)(e->ms * r), cudaMemcpyHostToDevice, e->st));
+        k_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(tmp.p, e->H, r, e->ms);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+        DN_CUDA(cudaStreamSynchronize(e->st));
+    }
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    e->have_factors = true;
+    return DNPEFF_OK;
+}
+
+int dnpeff_get_w(dnpeff_engine* e, float* out) {
+    DN_TRY(check_ready(e, true));
+    DeviceGuard g(e->device);
+    if (e->n > 0)
+        DN_CUDA(cudaMemcpyAsync(out, e->W, sizeof(float) * (size_t)(e->n * e->p.rank), cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    return DNPEFF_OK;
+}
+
+int dnpeff_get_h(dnpeff_engine* e, float* out) {
+    DN_TRY(check_ready(e, true));
+    DeviceGuard g(e->device);
+    const int r = e->p.rank;
+    if (e->ms > 0) {
+        DevBuf<float> tmp;
+        float* t = e->WA;
+        if (!t) {
+            DN_TRY(tmp.alloc((size_t)(e->ms * r)));
+            t = tmp.p;
+        }
+        k_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(e->H, t, e->ms, r);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+        DN_CUDA(cudaMemcpyAsync(out, t, sizeof(float) * (size_t)(e->ms * r), cudaMemcpyDeviceToHost, e->st));
+        DN_CUDA(cudaStreamSynchronize(e->st));
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_nccl_unique_id(void* id128) {
+    if (!id128) return fail(DNPEFF_ERR_INVALID, "null argument");
+    DN_TRY(nccl_load());
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is expected to be 128 bytes");
+    ncclUniqueId id;
+    DN_NCCL(nccl_api().GetUniqueId(&id));
+    memcpy(id128, &id, 128);
+    return DNPEFF_OK;
+}
+
+int dnpeff_comm_init(dnpeff_engine* e, const void* id128, int comm_rank, int comm_size) {
+    if (!e || !id128) return fail(DNPEFF_ERR_INVALID, "null argument");
+    if (comm_size != e->p.n_shards || comm_rank != e->p.shard_index)
+        return fail(DNPEFF_ERR_INVALID, "communicator rank/size must equal shard_index/n_shards");
+    DeviceGuard g(e->device);
+    DN_TRY(nccl_load());
+    ncclUniqueId id;
+    memcpy(&id, id128, 128);
+    DN_NCCL(nccl_api().CommInitRank(&e->comm, comm_size, id, comm_rank));
+    e->comm_rank = comm_rank;
+    e->comm_size = comm_size;
+    e->a_sq_global = -1.0;
+    return DNPEFF_OK;
+}
+
+int dnpeff_step_w(dnpeff_engine* e) {
+    DN_TRY(check_ready(e, true));
+    DeviceGuard g(e->device);
+    if (e->p.n_shards > 1 && e->comm_size != e->p.n_shards)
+        return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init");
+    return step_w(e);
+}
+
+int dnpeff_step_h(dnpeff_engine* e) {
+    DN_TRY(check_ready(e, true));
+    DeviceGuard g(e->device);
+    return step_h(e);
+}
+
+int dnpeff_synchronize(dnpeff_engine* e) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    DeviceGuard g(e->device);
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    return DNPEFF_OK;
+}
+
+int dnpeff_loss(dnpeff_engine* e, double* out) {
+    DN_TRY(check_ready(e, true));
+    if (!out) return fail(DNPEFF_ERR_INVALID, "null argument");
+    DeviceGuard g(e->device);
+    if (e->p.n_shards > 1 && e->comm_size != e->p.n_shards)
+        return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init");
+    return loss_from_current(e, true, out);
+}
+
+int dnpeff_run(dnpeff_engine* e, int32_t iters, int32_t log_every) {
+    DN_TRY(check_ready(e, true));
+    DeviceGuard g(e->device);
+    if (e->p.n_shards > 1 && e->comm_size != e->p.n_shards)
+        return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init");
+    auto t0 = std::chrono::high_resolution_clock::now();
+    for (int step = 0; step < iters; step++) {
+        DN_TRY(step_w(e));
+        DN_TRY(step_h(e));
+        // "step N: <loss> [<ms> ms/step]" every log_every steps, loss time
+        // excluded from the rate (multi_mu_dense_factors_nmf1.h:187-201).
+        if (log_every > 0 && (step + 1) % log_every == 0) {
+            DN_CUDA(cudaStreamSynchronize(e->st));
+            auto t1 = std::chrono::high_resolution_clock::now();
+            double ms = std::chrono::duration<double, std::milli>(t1 - t0).count();
+            double loss = 0;
+            DN_TRY(loss_from_current(e, true, &loss));
+            if (e->comm_rank == 0) {
+                printf("step %d: %g [%g ms/step]\n", step + 1, loss, ms / (double)log_every);
+                fflush(stdout);
+            }
+            t0 = std::chrono::high_resolution_clock::now();
+        }
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_fit_w_only(dnpeff_engine* e, int32_t iters, double* loss) {
+    DN_TRY(check_ready(e, true));
+    DeviceGuard g(e->device);
+    if (e->p.n_shards > 1 && e->comm_size != e->p.n_shards)
+        return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init");
+    const int r = e->p.rank;
+    DN_TRY(compute_ah_hh(e));
+    for (int it = 0; it < iters; it++) {
+        ScopedTimer t(e, 3);
+        DN_TRY(mu_update_launch(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->st));
+    }
+    if (loss) DN_TRY(loss_from_current(e, false, loss));
+    return DNPEFF_OK;
+}
+
+int dnpeff_enable_timing(dnpeff_engine* e, int enable) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    e->timing = enable != 0;
+    return DNPEFF_OK;
+}
+
+int dnpeff_get_timing(dnpeff_engine* e, double ms_total[DNPEFF_N_TIMERS], int64_t launches[DNPEFF_N_TIMERS]) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    DeviceGuard g(e->device);
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    for (auto& r : e->regions) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+            e->t_ms[r.id] += ms;
+            e->t_n[r.id] += 1;
+        }
+        e->ev_pool.push_back(r.a);
+        e->ev_pool.push_back(r.b);
+    }
+    e->regions.clear();
+    for (int i = 0; i < DNPEFF_N_TIMERS; i++) {
+        if (ms_total) ms_total[i] = e->t_ms[i];
+        if (launches) launches[i] = e->t_n[i];
+        e->t_ms[i] = 0;
+        e->t_n[i] = 0;
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_launch_count(dnpeff_engine* e, int64_t* out) {
+    if (!e || !out) return fail(DNPEFF_ERR_INVALID, "null argument");
+    *out = launch_counter() - e->launches0;
+    return DNPEFF_OK;
+}
+
+// ---- single kernels ---------------------------------------------------------
+int dnpeff_op_spmm(const float* vals, const int32_t* ind, const int64_t* ptr, int64_t rows,
+                   const float* D, int32_t r, float* out, void* stream) {
+    if (rows < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
+    cudaStream_t st = (cudaStream_t)stream;
+    SpmmPlan plan;
+    plan.n_short = rows;
+    if (spmm_fast_rank(r)) DN_TRY(spmm_make_plan(ptr, rows, &plan, st));
+    int s = spmm_dispatch(vals, ind, ptr, rows, D, r, out, plan, st);
+    if (plan.long_list) {
+        cudaStreamSynchronize(st);
+        cudaFree(plan.long_list);
+    }
+    return s;
+}
+
+int dnpeff_op_gram(const float* X, int64_t rows, int32_t r, float* G, void* stream) {
+    if (rows < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
+    float* scratch = nullptr;
+    DN_TRY(op_scratch(gram_plan(rows, r).scratch_floats, &scratch));
+    return gram_launch(X, rows, r, G, scratch, (cudaStream_t)stream);
+}
+
+int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows, int32_t r,
+                        float eps, void* stream) {
+    if (rows < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
+    return mu_update_launch(X, Num, G, rows, r, eps, (cudaStream_t)stream);
+}
+
+}  // extern "C"

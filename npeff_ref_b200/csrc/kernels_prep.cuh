@@ -1,0 +1,324 @@
+// Loader kernels: column counting, pruning map, shard extraction, CSC build,
+// plus the small elementwise helpers (init, transpose, reductions).
+// These are integer/byte passes bound by HBM bandwidth; every index is 64-bit
+// because nnz and rank*n_cols exceed 2^31 at the large configurations.
+#pragma once
+#include "common.cuh"
+
+namespace dnpeff {
+
+enum : int { kErrColRange = 1, kErrDuplicate = 2, kErrRowPtr = 4 };
+
+// Row i of the input owns [rowptr[i], rowptr[i+1]) or, with rowptr == NULL,
+// [i*k, (i+1)*k): the implicit offsets of a D-PEF file (src/io/pef_fisher_h5.h:175-177).
+__device__ __forceinline__ void row_range(const int64_t* rowptr, int64_t k, int64_t row,
+                                          int64_t& b, int64_t& e) {
+    if (rowptr) { b = rowptr[row]; e = rowptr[row + 1]; }
+    else { b = row * k; e = b + k; }
+}
+
+// colMask[csrColIndA[i]] += 1 of removeSmallestL0NormColumns_inPlace
+// (src/util/sparse_util.h:95-98), as integer atomics (order-independent).
+__global__ void k_count_columns(const int32_t* __restrict__ colind, int64_t nnz, int64_t n_cols,
+                                int32_t* __restrict__ counts, int* __restrict__ err) {
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < nnz; p += stride) {
+        int32_t c = __ldcs(colind + p);
+        if ((uint32_t)c >= (uint64_t)n_cols) atomicOr(err, kErrColRange);
+        else atomicAdd(counts + c, 1);
+    }
+}
+
+// keep[c] = counts[c] >= min  (src/util/sparse_util.h:110-118)
+__global__ void k_keep_flags(const int32_t* __restrict__ counts, int64_t n_cols, int32_t min_count,
+                             int32_t* __restrict__ flags) {
+    int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < n_cols) flags[c] = counts[c] >= min_count ? 1 : 0;
+}
+
+// ---- exclusive scan (1024 threads x 4 items per block) ----------------------
+template <typename TIn>
+__global__ void k_scan_block(const TIn* __restrict__ in, int64_t* __restrict__ out,
+                             int64_t* __restrict__ block_sums, int64_t N) {
+    __shared__ int64_t wsum[32];
+    int64_t base = ((int64_t)blockIdx.x * 1024 + threadIdx.x) * 4;
+    int64_t v[4];
+    int64_t s = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[i] = (base + i < N) ? (int64_t)in[base + i] : 0;
+        s += v[i];
+    }
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int64_t inc = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int64_t t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) wsum[w] = inc;
+    __syncthreads();
+    if (w == 0) {
+        int64_t x = wsum[lane];
+        int64_t xi = x;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int64_t t = __shfl_up_sync(0xffffffffu, xi, o);
+            if (lane >= o) xi += t;
+        }
+        wsum[lane] = xi - x;  // exclusive prefix of warp sums
+        if (lane == 31 && block_sums) block_sums[blockIdx.x] = xi;
+    }
+    __syncthreads();
+    int64_t run = wsum[w] + inc - s;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (base + i < N) out[base + i] = run;
+        run += v[i];
+    }
+}
+
+__global__ void k_scan_add(int64_t* __restrict__ out, const int64_t* __restrict__ block_prefix,
+                           int64_t N) {
+    int64_t base = ((int64_t)blockIdx.x * 1024 + threadIdx.x) * 4;
+    int64_t add = block_prefix[blockIdx.x];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+        if (base + i < N) out[base + i] += add;
+}
+
+// og_to_new / new_to_og of src/util/sparse_util.h:105-120 from the scanned flags.
+__global__ void k_build_maps(const int32_t* __restrict__ flags, const int64_t* __restrict__ pos,
+                             int64_t n_cols, int32_t* __restrict__ og_to_new,
+                             int32_t* __restrict__ new_to_og) {
+    int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n_cols) return;
+    if (flags[c]) {
+        og_to_new[c] = (int32_t)pos[c];
+        new_to_og[pos[c]] = (int32_t)c;
+    } else {
+        og_to_new[c] = -1;
+    }
+}
+
+// Entries of each row that fall into kept columns [c0, c0+w) of this shard:
+// the counting pass of splitColumnWise (src/util/matrix_util.h:39-44) merged
+// with the pruning test (src/util/sparse_util.h:139).  One block per row.
+__global__ void k_row_counts(const int32_t* __restrict__ colind, const int64_t* __restrict__ rowptr,
+                             int64_t k, int64_t n_rows, const int32_t* __restrict__ og_to_new,
+                             int64_t c0, int64_t w, int32_t* __restrict__ row_count,
+                             int* __restrict__ err) {
+    __shared__ int ws[32];
+    for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+        int64_t b, e;
+        row_range(rowptr, k, row, b, e);
+        if (e < b) { if (threadIdx.x == 0) atomicOr(err, kErrRowPtr); e = b; }
+        int cnt = 0;
+        for (int64_t p = b + threadIdx.x; p < e; p += blockDim.x) {
+            int64_t c = og_to_new[__ldcs(colind + p)];
+            cnt += (c >= c0 && c < c0 + w) ? 1 : 0;
+        }
+        cnt = warp_sum_i(cnt);
+        __syncthreads();
+        if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = cnt;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += ws[i];
+            row_count[row] = t;
+        }
+    }
+}
+
+// Order-preserving extraction of the shard's entries, with the row
+// normalisation val / (norm + 1e-9f) of src/io/pef_fisher_h5.h:38-52 applied on
+// the way and the column ids rebased to the shard start
+// (src/util/matrix_util.h:57-61).  One block of 256 threads per row.
+__global__ void k_extract_shard(const float* __restrict__ vals, const int32_t* __restrict__ colind,
+                                const int64_t* __restrict__ rowptr, int64_t k, int64_t n_rows,
+                                const float* __restrict__ norms,
+                                const int32_t* __restrict__ og_to_new, int64_t c0, int64_t w,
+                                const int64_t* __restrict__ out_rowptr, float* __restrict__ out_vals,
+                                int32_t* __restrict__ out_colind) {
+    __shared__ int wtot[8];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+        int64_t b, e;
+        row_range(rowptr, k, row, b, e);
+        if (e < b) e = b;
+        float denom = norms ? (norms[row] + 1e-9f) : 1.0f;
+        int64_t run = out_rowptr[row];
+        for (int64_t base = b; base < e; base += 256) {
+            int64_t p = base + threadIdx.x;
+            bool keep = false;
+            int64_t c = 0;
+            float v = 0.f;
+            if (p < e) {
+                c = og_to_new[__ldcs(colind + p)];
+                keep = (c >= c0 && c < c0 + w);
+                v = __ldcs(vals + p);
+            }
+            unsigned bal = __ballot_sync(0xffffffffu, keep);
+            if (lane == 0) wtot[wid] = __popc(bal);
+            __syncthreads();
+            int before = 0, total = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                int t = wtot[i];
+                before += (i < wid) ? t : 0;
+                total += t;
+            }
+            if (keep) {
+                int64_t q = run + before + __popc(bal & ((1u << lane) - 1u));
+                out_colind[q] = (int32_t)(c - c0);
+                out_vals[q] = norms ? v / denom : v;
+            }
+            run += total;
+            __syncthreads();
+        }
+    }
+}
+
+__global__ void k_max_rowlen(const int64_t* __restrict__ rowptr, int64_t n_rows,
+                             unsigned long long* __restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_rows) atomicMax(out, (unsigned long long)(rowptr[i + 1] - rowptr[i]));
+}
+
+// cnt_s[j] = counts[new_to_og[c0 + j]]: every stored entry of a kept column
+// survives, so the pruning counts are also the shard's column lengths.
+__global__ void k_gather_counts(const int32_t* __restrict__ counts,
+                                const int32_t* __restrict__ new_to_og, int64_t c0, int64_t w,
+                                int32_t* __restrict__ cnt_s) {
+    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < w) cnt_s[j] = counts[new_to_og[c0 + j]];
+    else if (j == w) cnt_s[j] = 0;
+}
+
+// ---- CSC build --------------------------------------------------------------
+// A stable transpose (rows ascending inside every column) without a sort: rows
+// are taken in waves of 64; inside a wave every column collects a 64-bit mask
+// of the wave rows that hold it (atomicOr: order-independent), an entry's slot
+// is colptr + entries placed by earlier waves + popcount of the lower mask
+// bits.  Deterministic, integer atomics only.  grid = (ceil(maxlen/256), 64).
+__global__ void k_csc_mark(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
+                           int64_t row_base, int64_t n_rows,
+                           unsigned long long* __restrict__ mask, int* __restrict__ err) {
+    int64_t row = row_base + blockIdx.y;
+    if (row >= n_rows) return;
+    int64_t p = rowptr[row] + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= rowptr[row + 1]) return;
+    unsigned long long bit = 1ull << blockIdx.y;
+    unsigned long long old = atomicOr(mask + colind[p], bit);
+    if (old & bit) atomicOr(err, kErrDuplicate);
+}
+
+__global__ void k_csc_place(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
+                            const float* __restrict__ vals, int64_t row_base, int64_t n_rows,
+                            const unsigned long long* __restrict__ mask,
+                            const int64_t* __restrict__ colptr, const int32_t* __restrict__ cursor,
+                            float* __restrict__ cvals, int32_t* __restrict__ crow) {
+    int64_t row = row_base + blockIdx.y;
+    if (row >= n_rows) return;
+    int64_t p = rowptr[row] + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= rowptr[row + 1]) return;
+    int32_t j = colind[p];
+    unsigned long long bit = 1ull << blockIdx.y;
+    int64_t q = colptr[j] + cursor[j] + __popcll(mask[j] & (bit - 1ull));
+    cvals[q] = vals[p];
+    crow[q] = (int32_t)row;
+}
+
+__global__ void k_csc_advance(const int64_t* __restrict__ rowptr,
+                              const int32_t* __restrict__ colind, int64_t row_base, int64_t n_rows,
+                              unsigned long long* __restrict__ mask, int32_t* __restrict__ cursor) {
+    int64_t row = row_base + blockIdx.y;
+    if (row >= n_rows) return;
+    int64_t p = rowptr[row] + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= rowptr[row + 1]) return;
+    int32_t j = colind[p];
+    unsigned long long mk = mask[j];
+    // Only the entry of the highest wave row of this column advances it; any
+    // other entry sees either the full mask or the cleared one, never "highest".
+    if ((mk >> blockIdx.y) == 1ull) {
+        cursor[j] += __popcll(mk);
+        mask[j] = 0ull;
+    }
+}
+
+// ---- reductions over the stored values --------------------------------------
+// partial[b] = (sum v, sum v*v) of block b, then one block folds the partials in
+// index order: double accumulation, fixed order.
+__global__ void k_sum_sumsq(const float* __restrict__ v, int64_t count, double* __restrict__ partial) {
+    __shared__ double sm[32];
+    double s = 0.0, q = 0.0;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        double x = (double)v[i];
+        s += x;
+        q += x * x;
+    }
+    double ts = block_sum(s, sm);
+    double tq = block_sum(q, sm);
+    if (threadIdx.x == 0) {
+        partial[2 * blockIdx.x] = ts;
+        partial[2 * blockIdx.x + 1] = tq;
+    }
+}
+
+// partial[b] = sum a[i]*b[i] over block b's grid-stride share (double).
+__global__ void k_dot(const float* __restrict__ a, const float* __restrict__ b, int64_t count,
+                      double* __restrict__ partial) {
+    __shared__ double sm[32];
+    double s = 0.0;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        s += (double)a[i] * (double)b[i];
+    double t = block_sum(s, sm);
+    if (threadIdx.x == 0) partial[blockIdx.x] = t;
+}
+
+// out[c] = sum_b partial[b*ncomp + c], one block, fixed order.
+__global__ void k_fold(const double* __restrict__ partial, int nblocks, int ncomp,
+                       double* __restrict__ out) {
+    __shared__ double sm[32];
+    for (int c = 0; c < ncomp; c++) {
+        double s = 0.0;
+        for (int b = threadIdx.x; b < nblocks; b += blockDim.x) s += partial[b * ncomp + c];
+        double t = block_sum(s, sm);
+        if (threadIdx.x == 0) out[c] = t;
+    }
+}
+
+// ---- factor helpers ---------------------------------------------------------
+__global__ void k_init_uniform(float* __restrict__ out, int64_t first, int64_t count, uint64_t key,
+                               float scale) {
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        out[i] = uniform01_from_key(key, (uint64_t)(first + i)) * scale;
+}
+
+// out[c, r] = in[r, c] for in of shape [rows, cols] (row-major both).  Used to
+// go between the file layout H[rank, n_cols] and the device layout [n_cols, rank]
+// (the reference does this on the host, src/util/matrices.h:49-62).
+__global__ void k_transpose(const float* __restrict__ in, float* __restrict__ out, int64_t rows,
+                            int64_t cols) {
+    __shared__ float tile[32][33];
+    int64_t tiles_c = (cols + 31) / 32;
+    int64_t tiles_r = (rows + 31) / 32;
+    for (int64_t t = blockIdx.x; t < tiles_c * tiles_r; t += gridDim.x) {
+        int64_t tr = t / tiles_c, tc = t % tiles_c;
+        for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+            int64_t r_ = tr * 32 + i, c_ = tc * 32 + threadIdx.x;
+            tile[i][threadIdx.x] = (r_ < rows && c_ < cols) ? in[r_ * cols + c_] : 0.f;
+        }
+        __syncthreads();
+        for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+            int64_t c_ = tc * 32 + i, r_ = tr * 32 + threadIdx.x;
+            if (c_ < cols && r_ < rows) out[c_ * rows + r_] = tile[threadIdx.x][i];
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace dnpeff

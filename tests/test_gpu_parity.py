@@ -1,0 +1,351 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU
+oracle on the same seeded inputs.  Integer / index work must be bit-exact;
+floating-point results must agree within the tolerances written beside each
+assert (the stated targets: factors 1e-4 relative Frobenius after 50 iterations
+from identical initial factors, loss 1e-5 relative)."""
+import ctypes as C
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from helpers import rel_fro, make_problem, oracle_preprocess, baseline_scale
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available()
+    torch.cuda.set_device(0)
+    return torch
+
+
+def _dev(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _engine(params, **kw):
+    from npeff_ref_b200 import MuNmf
+    return MuNmf(params, **kw)
+
+
+def _csr_random(rng, rows, cols, lens):
+    ptr = np.zeros(rows + 1, dtype=np.int64)
+    ptr[1:] = np.cumsum(lens)
+    ind = np.concatenate([rng.choice(cols, size=l, replace=False) for l in lens] +
+                         [np.zeros(0, dtype=np.int64)]).astype(np.int32)
+    vals = rng.random(int(ptr[-1]), dtype=np.float32)
+    return vals, ind, ptr
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("r", [4, 8, 32, 48, 64, 128, 256, 512, 5, 130])
+def test_op_spmm_matches_oracle(torch_cuda, r):
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    rng = np.random.default_rng(r)
+    rows, cols = 300, 900
+    # empty rows, rows of 1, rows around the 32-entry chunk, rows past the
+    # warp/block threshold (1024) with ragged tails
+    lens = rng.integers(0, 70, size=rows)
+    lens[:8] = [0, 1, 31, 32, 33, 900, 700, 0]
+    vals, ind, ptr = _csr_random(rng, rows, cols, lens)
+    big_cols = 5000
+    lens2 = np.array([0, 1025, 4097, 3000, 1024, 5000], dtype=np.int64)
+    v2, i2, p2 = _csr_random(rng, len(lens2), big_cols, lens2)
+    for (va, ia, pa, nc) in ((vals, ind, ptr, cols), (v2, i2, p2, big_cols)):
+        D = rng.random((nc, r), dtype=np.float32)
+        want = O.spmm(va, ia, pa, D, acc64=True)
+        out = torch.full((len(pa) - 1, r), float("nan"), device="cuda")
+        dv, di, dp, dD = _dev(torch, va), _dev(torch, ia), _dev(torch, pa), _dev(torch, D)
+        st = torch.cuda.current_stream().cuda_stream
+        check(lib().dnpeff_op_spmm(dv.data_ptr(), di.data_ptr(), dp.data_ptr(), len(pa) - 1,
+                                   dD.data_ptr(), r, out.data_ptr(), st))
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        # fp32 accumulation of <= 5000 positive terms against float64: 2e-6 relative
+        assert np.allclose(got, want, rtol=2e-6, atol=1e-7), np.abs(got - want).max()
+        # repeatable bit for bit
+        out2 = torch.empty_like(out)
+        check(lib().dnpeff_op_spmm(dv.data_ptr(), di.data_ptr(), dp.data_ptr(), len(pa) - 1,
+                                   dD.data_ptr(), r, out2.data_ptr(), st))
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("rows,r", [(1, 4), (1000, 32), (5000, 64), (777, 48), (20000, 128),
+                                    (3001, 256), (2500, 512), (100, 5), (0, 16)])
+def test_op_gram_matches_oracle(torch_cuda, rows, r):
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    rng = np.random.default_rng(rows + r)
+    X = rng.random((rows, r), dtype=np.float32)
+    want = O.gram(X, acc64=True) if rows > 0 else np.zeros((r, r), np.float32)
+    G = torch.full((r, r), float("nan"), device="cuda")
+    dX = _dev(torch, X) if rows > 0 else torch.zeros((1, r), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    check(lib().dnpeff_op_gram(dX.data_ptr(), rows, r, G.data_ptr(), st))
+    torch.cuda.synchronize()
+    got = G.cpu().numpy()
+    # fp32 partial sums folded in double: 3e-6 relative to the largest entry
+    assert np.abs(got - want).max() <= 3e-6 * max(np.abs(want).max(), 1e-30)
+    assert np.array_equal(got, got.T)
+
+
+@pytest.mark.parametrize("rows,r", [(1, 4), (513, 32), (300, 64), (1000, 48), (4099, 128),
+                                    (700, 256), (200, 512), (50, 5), (64, 516)])
+def test_op_mu_update_matches_oracle(torch_cuda, rows, r):
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    rng = np.random.default_rng(rows * 7 + r)
+    X = rng.random((rows, r), dtype=np.float32)
+    Num = rng.random((rows, r), dtype=np.float32)
+    B = rng.random((r + 3, r), dtype=np.float32)
+    G = (B.T @ B).astype(np.float32)
+    want = O.mu_update(X, Num, G, 1e-8, acc64=True)
+    dX, dN, dG = _dev(torch, X), _dev(torch, Num), _dev(torch, G)
+    st = torch.cuda.current_stream().cuda_stream
+    check(lib().dnpeff_op_mu_update(dX.data_ptr(), dN.data_ptr(), dG.data_ptr(), rows, r, 1e-8, st))
+    torch.cuda.synchronize()
+    got = dX.cpu().numpy()
+    # one fp32 dot of length r against float64, then the same fp32 elementwise rule
+    assert np.allclose(got, want, rtol=3e-6, atol=0), np.abs(got / want - 1).max()
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("min_count", [1, 2, 3])
+@pytest.mark.parametrize("n_shards", [1, 3])
+def test_loader_bit_exact(torch_cuda, min_count, n_shards):
+    """normalise -> prune -> column split -> CSR/CSC against the oracle, bit for bit."""
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k = 150, 2000, 70
+    vals, idx, norms = make_problem(n, m, k, seed=100 + min_count)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m, min_count)
+    mk = len(n2o)
+    for s in range(n_shards):
+        with _engine(MuNmfParams(rank=8), shard_index=s, n_shards=n_shards) as eng:
+            eng.set_csr(n, m, vals, idx, None, k, norms, min_count)
+            nn, mkept, c0, ms, nnz = eng.shape
+            assert (nn, mkept) == (n, mk)
+            assert (c0, ms) == O.split_range(mk, n_shards, s)
+            assert np.array_equal(eng.new_to_og(), n2o)
+            sv, sc, srp = O.split_columns(v, c, rp, c0, ms)
+            gv, gc, grp = eng.export_shard_csr()
+            assert nnz == len(sv)
+            assert np.array_equal(grp, srp)
+            assert np.array_equal(gc, sc)
+            assert np.array_equal(gv, sv)  # includes the fp32 division by (norm + 1e-9f)
+            cv, cr, cp = O.csr_to_csc(sv, sc, srp, ms)
+            hv, hr, hp = eng.export_shard_csc()
+            assert np.array_equal(hp, cp)
+            assert np.array_equal(hr, cr)
+            assert np.array_equal(hv, cv)
+            assert abs(eng.a_sq_norm() - float((sv.astype(np.float64) ** 2).sum())) < 1e-9 * max(nnz, 1)
+
+
+def test_loader_ragged_rows_and_empty_rows(torch_cuda):
+    from npeff_ref_b200 import MuNmfParams
+    rng = np.random.default_rng(5)
+    n, m = 130, 500
+    lens = rng.integers(0, 40, size=n)
+    lens[[0, 7, 129]] = 0
+    vals, ind, ptr = _csr_random(rng, n, m, lens)
+    v, c, rp, n2o = O.prune_columns(vals, ind, ptr, m, 2)
+    with _engine(MuNmfParams(rank=4)) as eng:
+        eng.set_csr(n, m, vals, ind, ptr, 0, None, 2)
+        assert np.array_equal(eng.new_to_og(), n2o)
+        gv, gc, grp = eng.export_shard_csr()
+        assert np.array_equal(grp, rp) and np.array_equal(gc, c) and np.array_equal(gv, v)
+        cv, cr, cp = O.csr_to_csc(v, c, rp, len(n2o))
+        hv, hr, hp = eng.export_shard_csc()
+        assert np.array_equal(hp, cp) and np.array_equal(hr, cr) and np.array_equal(hv, cv)
+
+
+def test_loader_rejects_bad_input(torch_cuda):
+    from npeff_ref_b200 import MuNmfParams, DnpeffError
+    with _engine(MuNmfParams(rank=4)) as eng:
+        vals = np.ones(6, np.float32)
+        with pytest.raises(DnpeffError) as ei:
+            eng.set_csr(2, 10, vals, np.array([0, 1, 2, 3, 4, 10], np.int32), None, 3)
+        assert ei.value.code == -4
+        eng.set_csr(2, 10, vals, np.array([0, 1, 1, 3, 4, 5], np.int32), None, 3)
+        eng.init_factors()
+        eng.step_w()
+        with pytest.raises(DnpeffError) as ei:  # duplicate column inside a row
+            eng.step_h()
+        assert ei.value.code == -4
+
+
+def test_seeded_init_bit_exact(torch_cuda):
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k, r = 40, 300, 20, 8
+    vals, idx, norms = make_problem(n, m, k, seed=1)
+    for s in range(2):
+        with _engine(MuNmfParams(rank=r, seed=99, init_scale=0.25), shard_index=s, n_shards=2) as eng:
+            eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+            eng.init_factors()
+            _, mk, c0, ms, _ = eng.shape
+            W0, H0 = O.init_factors(n, ms, r, 99, 0.25, col_start=c0)
+            assert np.array_equal(eng.load_w_to_host(), W0)
+            assert np.array_equal(eng.load_h_to_host(), H0)
+
+
+# ---------------------------------------------------------------------------
+CASES = [
+    # n, m, k, r, iters, eps
+    (64, 700, 40, 8, 50, 1e-12),
+    (256, 6000, 300, 32, 50, 1e-12),     # BASELINE config 1's shape, scaled down 8x
+    (96, 9000, 1500, 128, 50, 1e-8),     # long rows (block kernel), r = 128
+    (80, 3000, 200, 20, 30, 1e-8),       # rank not a power of two
+    (50, 400, 30, 7, 20, 1e-8),          # odd rank: generic kernels
+]
+
+
+@pytest.mark.parametrize("n,m,k,r,iters,eps", CASES)
+def test_full_run_matches_oracle(torch_cuda, n, m, k, r, iters, eps):
+    from npeff_ref_b200 import MuNmfParams
+    vals, idx, norms = make_problem(n, m, k, seed=n + r)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    scale = baseline_scale(v, n, mk, r)
+    with _engine(MuNmfParams(rank=r, eps=eps, seed=0, init_scale=scale)) as eng:
+        eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+        eng.init_factors()
+        W0, H0 = eng.load_w_to_host(), eng.load_h_to_host()
+        Wo0, Ho0 = O.init_factors(n, mk, r, 0, scale)
+        assert np.array_equal(W0, Wo0) and np.array_equal(H0, Ho0)
+        l0 = eng.compute_uncached_loss()
+        assert abs(l0 - O.loss(v, c, rp, mk, W0, H0)) < 1e-5 * l0
+        # single half steps
+        eng.step_w()
+        W1 = eng.load_w_to_host()
+        assert rel_fro(W1, O.step_w(v, c, rp, mk, W0, H0, eps)) < 2e-6
+        eng.step_h()
+        H1 = eng.load_h_to_host()
+        assert rel_fro(H1, O.step_h(v, c, rp, mk, W1, H0, eps)) < 2e-6
+        # full run from identical initial factors
+        eng.init_factors(W0, H0)
+        eng.run(iters, log_every=0)
+        W, H = eng.load_w_to_host(), eng.load_h_to_host()
+        Wo, Ho, ls = O.run(v, c, rp, mk, W0, H0, iters, eps, acc64=True, losses=True)
+        assert rel_fro(W, Wo) < 1e-4, rel_fro(W, Wo)      # stated target
+        assert rel_fro(H, Ho) < 1e-4, rel_fro(H, Ho)
+        l = eng.compute_uncached_loss()
+        assert abs(l - ls[-1]) < 1e-5 * ls[-1]            # stated target
+        assert np.all(np.isfinite(W)) and np.all(np.isfinite(H))
+        assert W.min() >= 0 and H.min() >= 0
+
+
+def test_run_is_repeatable_bit_for_bit(torch_cuda):
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k, r = 128, 4000, 1200, 64
+    vals, idx, norms = make_problem(n, m, k, seed=77)
+    outs = []
+    for _ in range(2):
+        with _engine(MuNmfParams(rank=r, eps=1e-8, seed=5, init_scale=0.01)) as eng:
+            eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+            eng.init_factors()
+            eng.run(10, log_every=0)
+            outs.append((eng.load_w_to_host(), eng.load_h_to_host()))
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+
+
+def test_fit_w_only_matches_oracle(torch_cuda):
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k, r = 300, 2000, 100, 32
+    vals, idx, norms = make_problem(n, m, k, seed=31)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    rng = np.random.default_rng(3)
+    W0, H0 = O.init_factors(n, mk, r, 3, 1.0)
+    H0 = (H0 * (rng.random(H0.shape) > 0.9)).astype(np.float32)  # 90 % of H zeroed
+    with _engine(MuNmfParams(rank=r, eps=1e-7)) as eng:
+        eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+        eng.init_factors(W0, H0)
+        loss = eng.fit_w_only(200)
+        W = eng.load_w_to_host()
+    Wo, lo = O.fit_w_only(v, c, rp, mk, W0, H0, 200, 1e-7)
+    assert rel_fro(W, Wo) < 1e-4
+    assert abs(loss - lo) < 1e-5 * lo
+
+
+def test_sharded_engines_match_unsharded_w_update(torch_cuda):
+    """Two shards on one device, the exchange emulated on the host: the summed
+    partial A_d*H_d^T / H_d*H_d^T give the unsharded W update (column sharding
+    needs no other exchange; the H update is local to a shard)."""
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k, r, eps = 100, 3000, 150, 16, 1e-8
+    vals, idx, norms = make_problem(n, m, k, seed=55)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    W0, H0 = O.init_factors(n, mk, r, 9, 0.05)
+    Hs = []
+    for s in range(2):
+        with _engine(MuNmfParams(rank=r, eps=eps, seed=9, init_scale=0.05), shard_index=s, n_shards=2) as eng:
+            eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+            eng.init_factors()
+            _, _, c0, ms, _ = eng.shape
+            assert np.array_equal(eng.load_h_to_host(), H0[:, c0:c0 + ms])
+            # H update needs only the shard: run it with the oracle's new W
+            W1 = O.step_w(v, c, rp, mk, W0, H0, eps)
+            eng.init_factors(W1, H0[:, c0:c0 + ms])
+            eng.step_h()
+            Hs.append(eng.load_h_to_host())
+    H1 = O.step_h(v, c, rp, mk, W1, H0, eps)
+    assert rel_fro(np.concatenate(Hs, axis=1), H1) < 2e-6
+
+
+def test_synthetic_generator_properties(torch_cuda):
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    n, m, k = 64, 50000, 2048
+    vals = torch.empty((n, k), dtype=torch.float32, device="cuda")
+    idx = torch.empty((n, k), dtype=torch.int32, device="cuda")
+    norms = torch.empty((n,), dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        check(lib().dnpeff_synth_pef_device(n, m, k, 1.1, 1.0, 7, vals.data_ptr(), idx.data_ptr(),
+                                            norms.data_ptr(), st))
+    v, i, nr = vals.cpu().numpy(), idx.cpu().numpy(), norms.cpu().numpy()
+    assert i.min() >= 0 and i.max() < m
+    for row in range(n):
+        assert len(np.unique(i[row])) == k                      # distinct columns
+        assert np.all(np.diff(v[row]) <= 0) and v[row, -1] >= 0  # descending, non-negative
+    assert np.allclose(nr, np.sqrt((v.astype(np.float64) ** 2).sum(1)), rtol=1e-6)
+    # Zipf: the most popular columns are in (nearly) every row
+    assert np.mean([(0 in set(r_)) for r_ in i]) > 0.95
+    vals2 = torch.empty_like(vals)
+    idx2 = torch.empty_like(idx)
+    check(lib().dnpeff_synth_pef_device(n, m, k, 1.1, 1.0, 7, vals2.data_ptr(), idx2.data_ptr(),
+                                        norms.data_ptr(), st))
+    assert torch.equal(vals, vals2) and torch.equal(idx, idx2)  # deterministic in the seed
+
+
+# ---- fixtures recorded from the reference engine ------------------------------
+_REF_CASES = sorted(glob.glob(os.path.join(GOLDEN, "ref_case_*.npz")))
+
+
+@pytest.mark.skipif(not _REF_CASES, reason="no reference-engine fixtures recorded yet")
+@pytest.mark.parametrize("path", _REF_CASES, ids=[os.path.basename(p) for p in _REF_CASES])
+def test_engine_matches_reference_engine_fixture(torch_cuda, path):
+    from npeff_ref_b200 import MuNmfParams
+    g = np.load(path)
+    n, m, k, r = int(g["n"]), int(g["m"]), int(g["k"]), int(g["rank"])
+    with _engine(MuNmfParams(rank=r, eps=float(g["eps"]))) as eng:
+        eng.set_csr(n, m, g["in_vals"], g["in_col"], None, k, None, int(g["min_count"]))
+        assert np.array_equal(eng.new_to_og(), g["new_to_og"])
+        gv, gc, grp = eng.export_shard_csr()
+        assert np.array_equal(grp, g["p_rowptr"].astype(np.int64))
+        assert np.array_equal(gc, g["p_col"]) and np.array_equal(gv, g["p_vals"])
+        eng.init_factors(g["W0"], g["H0"])
+        eng.run(int(g["iters"]), log_every=0)
+        assert rel_fro(eng.load_w_to_host(), g["W"]) < 1e-4
+        assert rel_fro(eng.load_h_to_host(), g["H"]) < 1e-4
+        l = eng.compute_uncached_loss()
+        assert abs(l - float(g["loss"])) < 1e-3 * l   # the reference sums its loss terms in fp32

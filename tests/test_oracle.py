@@ -1,0 +1,177 @@
+"""CPU-only checks of the oracle: against the reference's own known-answer
+pruning cases, against an independent float64 numpy rendering, and against the
+fixtures recorded from the reference engine."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from helpers import rel_fro, make_problem, oracle_preprocess, baseline_scale
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _csr_from_dense(d):
+    d = np.asarray(d, dtype=np.float32)
+    rp, ci, va = [0], [], []
+    for row in d:
+        nz = np.nonzero(row)[0]
+        ci += list(nz)
+        va += list(row[nz])
+        rp.append(len(ci))
+    return np.array(va, np.float32), np.array(ci, np.int32), np.array(rp, np.int64)
+
+
+# The four cases of cc/cuda_lrm_npeff/src/preprocess/column_pruning_test.cc:12-105
+# (same pruning scheme as cc/cuda_d_npeff/src/util/sparse_util.h:79-159).
+_M1 = [[1, 0, 0, -4, 0], [0, 2, 0, -.5, 0], [0, 4, 0, -.5, 0]]
+_M2 = [[1, 0, 0, -4, 0], [0, 0, 1, 0, .5], [0, 4, 0, -.5, 0]]
+PRUNE_KAT = [
+    (_M1, 1, [[1, 0, -4], [0, 2, -.5], [0, 4, -.5]], [0, 1, 3]),
+    (_M1, 2, [[0, -4], [2, -.5], [4, -.5]], [1, 3]),
+    (_M1, 3, [[-4], [-.5], [-.5]], [3]),
+    (_M2, 2, [[-4], [0], [-.5]], [3]),  # a row emptied by pruning stays as an empty row
+]
+
+
+@pytest.mark.parametrize("dense,min_count,expected,new_to_old", PRUNE_KAT)
+def test_prune_known_answers(dense, min_count, expected, new_to_old):
+    va, ci, rp = _csr_from_dense(dense)
+    v2, c2, rp2, n2o = O.prune_columns(va, ci, rp, 5, min_count)
+    ev, ec, erp = _csr_from_dense(expected)
+    assert np.array_equal(n2o, np.array(new_to_old, np.int32))
+    assert np.array_equal(rp2, erp)
+    assert np.array_equal(c2, ec)
+    assert np.array_equal(v2, ev)
+
+
+def test_split_ranges_match_reference_rule():
+    # getSizeOfSplit: floor(total/n) each, the last takes the remainder
+    assert [O.split_range(10, 3, i) for i in range(3)] == [(0, 3), (3, 3), (6, 4)]
+    assert [O.split_range(8, 4, i) for i in range(4)] == [(0, 2), (2, 2), (4, 2), (6, 2)]
+    assert O.split_range(5, 1, 0) == (0, 5)
+
+
+def test_split_columns_partitions_matrix():
+    vals, idx, norms = make_problem(20, 97, 13, seed=3)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, 97)
+    m = len(n2o)
+    total = 0
+    for s in range(3):
+        c0, w = O.split_range(m, 3, s)
+        sv, sc, srp = O.split_columns(v, c, rp, c0, w)
+        total += len(sv)
+        assert sc.min(initial=0) >= 0 and sc.max(initial=0) < w
+        # within-row order preserved
+        for i in range(20):
+            row = c[rp[i]:rp[i + 1]]
+            keep = (row >= c0) & (row < c0 + w)
+            assert np.array_equal(sc[srp[i]:srp[i + 1]], row[keep] - c0)
+    assert total == len(v)
+
+
+def test_csc_is_stable_transpose():
+    vals, idx, norms = make_problem(30, 64, 9, seed=5)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, 64)
+    m = len(n2o)
+    cv, cr, cp = O.csr_to_csc(v, c, rp, m)
+    rows = np.repeat(np.arange(30), np.diff(rp))
+    order = np.lexsort((rows, c))
+    assert np.array_equal(cr, rows[order])
+    assert np.array_equal(cv, v[order])
+    assert np.array_equal(np.diff(cp), np.bincount(c, minlength=m))
+
+
+def test_init_uniform_range_and_shard_invariance():
+    full = O.init_uniform(0, 1000, 42, 1, 0.5)
+    assert full.min() > 0 and full.max() <= 0.5
+    part = O.init_uniform(300, 200, 42, 1, 0.5)
+    assert np.array_equal(part, full[300:500])
+    assert not np.array_equal(O.init_uniform(0, 1000, 42, 0, 0.5), full)
+
+
+@pytest.mark.parametrize("n,m,k,r,eps", [(48, 300, 24, 6, 1e-12), (64, 512, 64, 8, 1e-8)])
+def test_oracle_matches_numpy_float64(n, m, k, r, eps):
+    vals, idx, norms = make_problem(n, m, k, seed=n)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    W0, H0 = O.init_factors(n, mk, r, 0, baseline_scale(v, n, mk, r))
+    Wn, Hn, ln = O.numpy_run(v, c, rp, mk, W0, H0, 30, eps)
+    W1, H1, l1 = O.run(v, c, rp, mk, W0, H0, 30, eps, acc64=True, losses=True)
+    # float32 storage against float64 everywhere: 1e-5 is ample, 1e-4 is the target
+    assert rel_fro(W1, Wn) < 1e-5 and rel_fro(H1, Hn) < 1e-5
+    assert np.max(np.abs(l1 - ln) / ln) < 1e-6
+    W2, H2, l2 = O.run(v, c, rp, mk, W0, H0, 30, eps, acc64=False, losses=True)
+    assert rel_fro(W2, Wn) < 1e-4 and rel_fro(H2, Hn) < 1e-4
+    assert np.max(np.abs(l2 - ln) / ln) < 1e-5
+    assert abs(O.loss(v, c, rp, mk, W1, H1) - l1[-1]) < 1e-9 * l1[-1]
+
+
+def test_fit_w_only_matches_numpy():
+    n, m, k, r = 40, 200, 16, 5
+    vals, idx, norms = make_problem(n, m, k, seed=9)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    W0, H0 = O.init_factors(n, mk, r, 3, 1.0)
+    rng = np.random.default_rng(0)
+    H0 = (H0 * (rng.random(H0.shape) > 0.9)).astype(np.float32)
+    A = np.zeros((n, mk))
+    np.add.at(A, (np.repeat(np.arange(n), np.diff(rp)), c), v.astype(np.float64))
+    W = W0.astype(np.float64)
+    AH, HH = A @ H0.T.astype(np.float64), H0.astype(np.float64) @ H0.T.astype(np.float64)
+    for _ in range(25):
+        W *= AH / (W @ HH + 1e-7)
+    Wo, lo = O.fit_w_only(v, c, rp, mk, W0, H0, 25, 1e-7)
+    assert rel_fro(Wo, W) < 1e-5
+    assert abs(lo - np.linalg.norm(A - W @ H0)) < 1e-5 * lo
+
+
+def test_sharded_update_equals_unsharded():
+    """Summing per-shard A_d*H_d^T and H_d*H_d^T partials reproduces the unsharded W update."""
+    n, m, k, r = 32, 240, 20, 4
+    vals, idx, norms = make_problem(n, m, k, seed=21)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    W0, H0 = O.init_factors(n, mk, r, 1, 0.1)
+    AH = np.zeros((n, r))
+    HH = np.zeros((r, r))
+    for s in range(3):
+        c0, w = O.split_range(mk, 3, s)
+        sv, sc, srp = O.split_columns(v, c, rp, c0, w)
+        Hs = H0[:, c0:c0 + w]
+        AH += O.spmm(sv, sc, srp, np.ascontiguousarray(Hs.T)).astype(np.float64)
+        HH += O.gram(np.ascontiguousarray(Hs.T)).astype(np.float64)
+    Wsh = O.mu_update(W0, AH.astype(np.float32), HH.astype(np.float32), 1e-8)
+    Wun = O.step_w(v, c, rp, mk, W0, H0, 1e-8)
+    assert rel_fro(Wsh, Wun) < 1e-6
+
+
+# ---- fixtures recorded from the reference engine itself ---------------------
+_REF_CASES = sorted(glob.glob(os.path.join(GOLDEN, "ref_case_*.npz")))
+
+
+@pytest.mark.skipif(not _REF_CASES, reason="no reference-engine fixtures recorded yet")
+@pytest.mark.parametrize("path", _REF_CASES, ids=[os.path.basename(p) for p in _REF_CASES])
+def test_oracle_matches_reference_engine(path):
+    g = np.load(path)
+    n, m, k, r = int(g["n"]), int(g["m"]), int(g["k"]), int(g["rank"])
+    rowptr = np.arange(n + 1, dtype=np.int64) * k
+    v, c, rp, n2o = O.prune_columns(g["in_vals"], g["in_col"], rowptr, m, int(g["min_count"]))
+    # integer work: bit-exact against removeSmallestL0NormColumns_inPlace
+    assert np.array_equal(n2o, g["new_to_og"])
+    assert np.array_equal(rp, g["p_rowptr"].astype(np.int64))
+    assert np.array_equal(c, g["p_col"])
+    assert np.array_equal(v, g["p_vals"])
+    mk = len(n2o)
+    # float work from the reference's own initial factors.  The reference sums
+    # in cuSPARSE/cuBLAS order in fp32; 1e-4 relative Frobenius is the stated bar.
+    W, H, ls = O.run(v, c, rp, mk, g["W0"], g["H0"], int(g["iters"]), float(g["eps"]),
+                     acc64=True, losses=True)
+    assert rel_fro(W, g["W"]) < 1e-4
+    assert rel_fro(H, g["H"]) < 1e-4
+    # the reference adds its three loss terms in fp32, so its printed loss
+    # carries ~1e-4 of cancellation noise; compare at 1e-3.
+    assert abs(ls[-1] - float(g["loss"])) < 1e-3 * ls[-1]
+    assert abs(O.loss(v, c, rp, mk, g["W0"], g["H0"]) - float(g["loss0"])) < 1e-3 * float(g["loss0"])
