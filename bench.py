@@ -81,13 +81,14 @@ class ClockSampler(threading.Thread):
                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
             }
-            while not self._stop_evt.is_set():
+            while True:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
                 mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
                 for bit, name in names.items():
                     if mask & bit:
                         self.reasons.add(name)
-                self._stop_evt.wait(0.2)
+                if self._stop_evt.wait(0.2):
+                    break
         except Exception as ex:  # no NVML: report that instead of clocks
             self.reasons.add("unsampled: %s" % type(ex).__name__)
 
@@ -239,7 +240,12 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     n, m, k, r = c["n"], c["m"], c["k"], c["r"]
     warm = max(args.warmup, 3)
-    stream = torch.cuda.current_stream().cuda_stream
+    # a side stream made current: the engine launches on it and torch's events,
+    # copies and collectives see the same stream (the legacy default stream is 0,
+    # which the C ABI reads as "make your own")
+    side = torch.cuda.Stream()
+    torch.cuda.set_stream(side)
+    stream = side.cuda_stream
 
     # ---- synthetic D-PEF arrays, generated in HBM (every rank: the same matrix)
     d_vals = torch.empty((n, k), dtype=torch.float32, device="cuda")

@@ -72,7 +72,7 @@ k_synth_rows(int64_t n, int64_t m, int k, const double* __restrict__ cdf, double
                         uint32_t b = 1u << (c & 31);
                         if (!(bitmap[c >> 5] & b)) {
                             bitmap[c >> 5] |= b;
-                            claimed[count++] = (int)c;
+                            count++;
                         }
                     }
                     s_count = count;
@@ -101,13 +101,11 @@ k_synth_rows(int64_t n, int64_t m, int k, const double* __restrict__ cdf, double
                 before += (i < wid) ? t : 0;
                 total += t;
             }
-            int slot = before + __popc(bal & ((1u << lane) - 1u));
-            if (count + total <= k) {
-                if (isnew) claimed[count + slot] = c;
-            } else {
+            if (count + total > k) {
                 // Last round overshoots: keep the (k - count) new columns with the
-                // smallest keyed hash, so the kept set does not depend on which
-                // thread won a repeated draw.
+                // smallest keyed hash.  The set of new columns of a round does not
+                // depend on which thread won a repeated draw, so neither does this.
+                int slot = before + __popc(bal & ((1u << lane) - 1u));
                 if (isnew) s_newcols[slot] = c;
                 __syncthreads();
                 if (isnew) {
@@ -118,13 +116,41 @@ k_synth_rows(int64_t n, int64_t m, int k, const double* __restrict__ cdf, double
                         uint64_t hv = mix64(rkey ^ (uint64_t)o);
                         rank += (hv < mine || (hv == mine && o < c)) ? 1 : 0;
                     }
-                    if (rank < k - count) claimed[count + rank] = c;
-                    else atomicAnd(bitmap + (c >> 5), ~bit);
+                    if (rank >= k - count) atomicAnd(bitmap + (c >> 5), ~bit);
                 }
                 total = k - count;
             }
             __syncthreads();
             if (tid == 0) s_count = count + total;
+            __syncthreads();
+        }
+        // ---- the claimed set in ascending column order (read back from the bitmap,
+        //      which is cleared on the way): independent of any thread timing --------
+        {
+            int64_t wpt = (bitmap_words + kSynthThreads - 1) / kSynthThreads;
+            int64_t w0 = (int64_t)tid * wpt;
+            int64_t w1 = w0 + wpt < bitmap_words ? w0 + wpt : bitmap_words;
+            int cnt = 0;
+            for (int64_t w = w0; w < w1; w++) cnt += __popc(bitmap[w]);
+            int inc = cnt;
+            for (int o = 1; o < 32; o <<= 1) {
+                int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
+            }
+            __syncthreads();
+            if (lane == 31) s_warp[wid] = inc;
+            __syncthreads();
+            int base = inc - cnt;
+            for (int i = 0; i < wid; i++) base += s_warp[i];
+            for (int64_t w = w0; w < w1; w++) {
+                uint32_t bitsw = bitmap[w];
+                if (bitsw) bitmap[w] = 0u;
+                while (bitsw) {
+                    int b = __ffs(bitsw) - 1;
+                    claimed[base++] = (int)(w * 32 + b);
+                    bitsw &= bitsw - 1u;
+                }
+            }
             __syncthreads();
         }
         // ---- values: descending order statistics of k chi-square(1) draws ---
@@ -173,12 +199,6 @@ k_synth_rows(int64_t n, int64_t m, int k, const double* __restrict__ cdf, double
         }
         double tot = block_sum(sq, s_red);
         if (tid == 0) out_norms[row] = (float)sqrt(tot);
-        __syncthreads();
-        // clear only the bits this row set
-        for (int j = tid; j < k; j += kSynthThreads) {
-            int c = claimed[j];
-            atomicAnd(bitmap + (c >> 5), ~(1u << (c & 31)));
-        }
         __syncthreads();
     }
 }
