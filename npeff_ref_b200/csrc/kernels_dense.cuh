@@ -114,7 +114,7 @@ k_gram_partial(const float* __restrict__ X, int64_t rows, int r, int ntile, int6
 }
 
 // G[a,b] = sum over slabs of the partial tile element, slabs in index order.
-__global__ void k_gram_reduce(const float* __restrict__ partial, int nslab, int npairs, int ntile,
+static __global__ void k_gram_reduce(const float* __restrict__ partial, int nslab, int npairs, int ntile,
                               int tile, int r, float* __restrict__ G) {
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= r * r) return;
@@ -155,10 +155,9 @@ inline GramPlan gram_plan(int64_t rows, int r) {
     return g;
 }
 
-// scratch must hold gram_plan(rows, r).scratch_floats floats.
-inline int gram_launch(const float* X, int64_t rows, int r, float* G, float* scratch,
-                       cudaStream_t st) {
-    GramPlan g = gram_plan(rows, r);
+// scratch must hold g.scratch_floats floats.
+inline int gram_launch_plan(const float* X, int64_t rows, int r, float* G, float* scratch,
+                            const GramPlan& g, cudaStream_t st) {
     dim3 grid(g.npairs, g.nslab);
     if (g.tile == 128)
         k_gram_partial<128><<<grid, 256, 0, st>>>(X, rows, r, g.ntile, g.rows_per_slab, scratch);
@@ -170,6 +169,12 @@ inline int gram_launch(const float* X, int64_t rows, int r, float* G, float* scr
     DN_LAUNCH_CHECK();
     DN_COUNT_LAUNCH(2);
     return DNPEFF_OK;
+}
+
+// scratch must hold gram_plan(rows, r).scratch_floats floats.
+inline int gram_launch(const float* X, int64_t rows, int r, float* G, float* scratch,
+                       cudaStream_t st) {
+    return gram_launch_plan(X, rows, r, G, scratch, gram_plan(rows, r), st);
 }
 
 // ---------------------------------------------------------------------------
@@ -266,7 +271,7 @@ k_mu_update(float* __restrict__ X, const float* __restrict__ Num, const float* _
 }
 
 // Any rank: one warp per row, the row cached in shared memory (r floats per warp).
-__global__ void k_mu_update_generic(float* __restrict__ X, const float* __restrict__ Num,
+static __global__ void k_mu_update_generic(float* __restrict__ X, const float* __restrict__ Num,
                                     const float* __restrict__ G, int64_t rows, int r, float eps) {
     extern __shared__ float xs_all[];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
