@@ -174,6 +174,26 @@ int dnpeff_op_gram(const float* X, int64_t rows, int32_t r, float* G, void* stre
 int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows, int32_t r,
                         float eps, void* stream);
 
+/* Allocation-free variant of dnpeff_op_gram (no counterpart in the reference).
+ *
+ * For callers that must not allocate device memory at call time: code running
+ * inside another framework's memory pool, a loop with a fixed memory budget, or
+ * any place where cudaMalloc's implicit device synchronisation is unacceptable.
+ * The slab partials go to a fixed DNPEFF_NOALLOC_SCRATCH_BYTES array that is part
+ * of the library image (every GPU that loads the library holds it until the
+ * process exits) instead of an allocated buffer; the call makes no cudaMalloc,
+ * cudaFree or other allocating call.  Inputs and outputs are the caller's, as
+ * for dnpeff_op_gram, and the result is the same.
+ *   - rank above DNPEFF_NOALLOC_MAX_RANK fails with DNPEFF_ERR_UNSUPPORTED;
+ *   - the first call on a device looks up the array's device address; make that
+ *     first call before starting any stream capture on that device;
+ *   - all calls on a device share the one array: calls that can overlap on the
+ *     GPU (different streams, different threads) race and must be serialised by
+ *     the caller.  Nothing in the array needs clearing between calls. */
+#define DNPEFF_NOALLOC_SCRATCH_BYTES (16 * 1024 * 1024)
+#define DNPEFF_NOALLOC_MAX_RANK 1024
+int dnpeff_op_gram_noalloc(const float* X, int64_t rows, int32_t r, float* G, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,6 +61,7 @@ SIGNATURES = {
     "dnpeff_op_spmm": (C.c_int, [_P, _P, _P, _I64, _P, _I32, _P, _P]),
     "dnpeff_op_gram": (C.c_int, [_P, _I64, _I32, _P, _P]),
     "dnpeff_op_mu_update": (C.c_int, [_P, _P, _P, _I64, _I32, C.c_float, _P]),
+    "dnpeff_op_gram_noalloc": (C.c_int, [_P, _I64, _I32, _P, _P]),
     "dnpeff_synth_pef_device": (C.c_int, [_I64, _I64, _I64, C.c_double, C.c_double, C.c_uint64,
                                           _P, _P, _P, _P]),
 }
