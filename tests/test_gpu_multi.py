@@ -1,0 +1,64 @@
+"""Multi-GPU parity: one engine per GPU (child processes), column shards joined
+by NCCL, against the unsharded CPU oracle.  Needs >= 2 CUDA devices."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+PROBLEM = dict(n=160, m=5000, k=220, r=32, eps=1e-8, iters=20, seed=23, scale=0.02)
+
+
+def _n_gpus():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+def _worker(rank, world, uid, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from npeff_ref_b200 import MuNmf, MuNmfParams
+    from helpers import make_problem
+    P = PROBLEM
+    vals, idx, norms = make_problem(P["n"], P["m"], P["k"], seed=P["seed"])
+    with MuNmf(MuNmfParams(rank=P["r"], eps=P["eps"], seed=3, init_scale=P["scale"]), device=rank,
+               shard_index=rank, n_shards=world) as eng:
+        eng.set_csr(P["n"], P["m"], vals, idx, None, P["k"], norms, 1)
+        eng.init_comm(uid)
+        eng.init_factors()
+        eng.run(P["iters"], log_every=0)
+        loss = eng.compute_uncached_loss()
+        np.savez(os.path.join(out_dir, "rank%d.npz" % rank), W=eng.load_w_to_host(),
+                 H=eng.load_h_to_host(), loss=loss, c0=eng.shape[2])
+
+
+@pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_nccl_sharded_run_matches_oracle(tmp_path, world):
+    if _n_gpus() < world:
+        pytest.skip("needs %d GPUs" % world)
+    import torch.multiprocessing as mp
+    from npeff_ref_b200 import MuNmf
+    from oracle import oracle as O
+    from helpers import make_problem, oracle_preprocess, rel_fro
+    uid = MuNmf.make_unique_id()
+    mp.spawn(_worker, args=(world, uid, str(tmp_path)), nprocs=world, join=True)
+    parts = [np.load(os.path.join(str(tmp_path), "rank%d.npz" % r)) for r in range(world)]
+    P = PROBLEM
+    vals, idx, norms = make_problem(P["n"], P["m"], P["k"], seed=P["seed"])
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, P["m"])
+    mk = len(n2o)
+    W0, H0 = O.init_factors(P["n"], mk, P["r"], 3, P["scale"])
+    W, H, ls = O.run(v, c, rp, mk, W0, H0, P["iters"], P["eps"], losses=True)
+    Hg = np.concatenate([p["H"] for p in sorted(parts, key=lambda p: int(p["c0"]))], axis=1)
+    for p in parts:                      # W is replicated and identical on every rank
+        assert np.array_equal(p["W"], parts[0]["W"])
+        assert abs(float(p["loss"]) - ls[-1]) < 1e-5 * ls[-1]
+    assert rel_fro(parts[0]["W"], W) < 1e-4
+    assert rel_fro(Hg, H) < 1e-4
