@@ -259,7 +259,8 @@ def main():
 
     def make_engine():
         return MuNmf(MuNmfParams(rank=r, eps=EPS, seed=c["seed"]), device=local_rank,
-                     shard_index=rank, n_shards=world, stream=stream)
+                     shard_index=rank, n_shards=world, stream=stream,
+                     shard_mode=MuNmf.CYCLIC if world > 1 else MuNmf.CONTIGUOUS)
 
     def join(eng):
         if world > 1:
@@ -394,7 +395,7 @@ def main():
             "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name(cfg_id, c), "n_cols_kept": m_kept,
-                       "nnz_per_rank": nnz, "shard": "columns/%d" % world,
+                       "nnz_per_rank": nnz, "shard": "columns/%d%s" % (world, " cyclic" if world > 1 else ""),
                        "l2": "inputs larger than L2 (A %.1f GB, H %.2f GB per rank)" % (
                            16.0 * nnz / 1e9, 4.0 * r * ms / 1e9),
                        "setup_s": {"generate": round(t_gen, 2), "load_resident": round(t_load, 2)},

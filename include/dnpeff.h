@@ -54,9 +54,20 @@ typedef struct {
     float eps;          /* added to the denominator; the executable hard-codes 1e-8f */
     uint64_t seed;      /* the executable hard-codes 43190432042 */
     float init_scale;   /* factors start as init_scale * U(0,1]; <= 0 means 1.0 (reference) */
-    int32_t shard_index; /* which column range of the kept columns this engine owns */
-    int32_t n_shards;    /* number of column ranges (== number of engines in the job) */
+    int32_t shard_index; /* which part of the kept columns this engine owns */
+    int32_t n_shards;    /* number of parts (== number of engines in the job) */
+    int32_t shard_mode;  /* DNPEFF_SHARD_CONTIGUOUS (reference) or DNPEFF_SHARD_CYCLIC */
 } dnpeff_params;
+
+/* How the kept columns are dealt to the engines of a job.
+ * CONTIGUOUS: equal-width ranges, the last takes the remainder -- splitColumnWise /
+ *   getSizeOfSplit (src/util/matrix_util.h:10-69); H shards concatenate in order.
+ * CYCLIC: engine d owns kept columns d, d+n_shards, ...; balances stored entries
+ *   when column popularity follows the column order (the reference's split puts
+ *   every popular column on engine 0).  dnpeff_get_shard_columns tells where each
+ *   local column of H belongs. */
+#define DNPEFF_SHARD_CONTIGUOUS 0
+#define DNPEFF_SHARD_CYCLIC 1
 
 const char* dnpeff_last_error(void);
 int dnpeff_abi_version(void);
@@ -98,6 +109,10 @@ int dnpeff_get_shape(dnpeff_engine* eng, int64_t* n_rows, int64_t* n_cols_kept,
                      int64_t* col_start, int64_t* n_cols_shard, int64_t* nnz_shard);
 /* newToOgIndex of removeSmallestL0NormColumns_inPlace: n_cols_kept original ids. */
 int dnpeff_get_new_to_og(dnpeff_engine* eng, int32_t* out);
+/* For each of the n_cols_shard local columns: its index among the kept columns
+ * (position in the full H / in reduce_kept_indices) and its original column id.
+ * Either output may be NULL. */
+int dnpeff_get_shard_columns(dnpeff_engine* eng, int32_t* kept_ids, int32_t* original_ids);
 /* The shard's CSR as splitColumnWise leaves it (bit-exact partition check). */
 int dnpeff_export_shard_csr(dnpeff_engine* eng, int64_t* rowptr, int32_t* colind, float* vals);
 /* The shard's CSC (values, row ids, n_cols_shard+1 offsets), rows ascending in a column. */

@@ -18,7 +18,8 @@ class DnpeffError(RuntimeError):
 
 class Params(C.Structure):
     _fields_ = [("rank", C.c_int32), ("eps", C.c_float), ("seed", C.c_uint64),
-                ("init_scale", C.c_float), ("shard_index", C.c_int32), ("n_shards", C.c_int32)]
+                ("init_scale", C.c_float), ("shard_index", C.c_int32), ("n_shards", C.c_int32),
+                ("shard_mode", C.c_int32)]
 
 
 def lib_path():
@@ -39,6 +40,7 @@ SIGNATURES = {
     "dnpeff_set_csr_device": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_get_shape": (C.c_int, [_P] + [C.POINTER(_I64)] * 5),
     "dnpeff_get_new_to_og": (C.c_int, [_P, _P]),
+    "dnpeff_get_shard_columns": (C.c_int, [_P, _P, _P]),
     "dnpeff_export_shard_csr": (C.c_int, [_P, _P, _P, _P]),
     "dnpeff_export_shard_csc": (C.c_int, [_P, _P, _P, _P]),
     "dnpeff_a_sq_norm": (C.c_int, [_P, C.POINTER(C.c_double)]),

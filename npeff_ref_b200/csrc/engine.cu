@@ -99,6 +99,7 @@ struct dnpeff_engine {
     bool own_stream = false;
 
     int64_t n = 0, m_full = 0, m_kept = 0, c0 = 0, ms = 0, nnz = 0;
+    ShardMap map = {0, 0, 1, 0, 0};
     bool loaded = false, have_factors = false, csc_ready = false;
 
     float* a_vals = nullptr;
@@ -273,7 +274,16 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
 
     // 3. this engine's range of kept columns
     int64_t c0 = 0, ms = 0;
-    shard_range(m_kept, e->p.n_shards, e->p.shard_index, &c0, &ms);
+    ShardMap map;
+    if (e->p.shard_mode == DNPEFF_SHARD_CYCLIC) {
+        int64_t G = e->p.n_shards, d = e->p.shard_index;
+        ms = m_kept > d ? (m_kept - d + G - 1) / G : 0;
+        c0 = d;
+        map = {c0, ms, (int32_t)G, (int32_t)d, 1};
+    } else {
+        shard_range(m_kept, e->p.n_shards, e->p.shard_index, &c0, &ms);
+        map = {c0, ms, 1, 0, 0};
+    }
 
     // 4. shard row lengths -> row offsets
     DevBuf<int32_t> row_count;
@@ -281,7 +291,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_CUDA(cudaMalloc((void**)&e->a_rowptr, sizeof(int64_t) * (size_t)(n + 1)));
     if (n > 0) {
         int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 32);
-        k_row_counts<<<(unsigned)blocks, 256, 0, st>>>(d_col, d_rowptr, k, n, og_to_new.p, c0, ms,
+        k_row_counts<<<(unsigned)blocks, 256, 0, st>>>(d_col, d_rowptr, k, n, og_to_new.p, map,
                                                       row_count.p, err.p);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
@@ -298,7 +308,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     if (n > 0) {
         int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 32);
         k_extract_shard<<<(unsigned)blocks, 256, 0, st>>>(d_vals, d_col, d_rowptr, k, n, d_norms,
-                                                         og_to_new.p, c0, ms, e->a_rowptr,
+                                                         og_to_new.p, map, e->a_rowptr,
                                                          e->a_vals, e->a_col);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
@@ -308,7 +318,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DevBuf<int32_t> cnt_s;
     DN_TRY(cnt_s.alloc((size_t)ms + 1));
     DN_CUDA(cudaMalloc((void**)&e->c_colptr, sizeof(int64_t) * (size_t)(ms + 1)));
-    k_gather_counts<<<(unsigned)ceil_div(ms + 1, 256), 256, 0, st>>>(counts.p, e->new_to_og, c0, ms, cnt_s.p);
+    k_gather_counts<<<(unsigned)ceil_div(ms + 1, 256), 256, 0, st>>>(counts.p, e->new_to_og, map, cnt_s.p);
     DN_LAUNCH_CHECK();
     DN_COUNT_LAUNCH(1);
     DN_TRY(scan_exclusive<int32_t>(cnt_s.p, e->c_colptr, ms + 1, st));
@@ -326,6 +336,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     e->a_sq = hs[1];
 
     e->n = n; e->m_full = m_full; e->m_kept = m_kept; e->c0 = c0; e->ms = ms; e->nnz = nnz;
+    e->map = map;
 
     // 8. factor and work buffers, long-row lists
     DN_CUDA(cudaMalloc((void**)&e->W, sizeof(float) * (size_t)std::max<int64_t>(n * r, 1)));
@@ -482,8 +493,8 @@ int init_generated(dnpeff_engine* e, bool do_w, bool do_h) {
         DN_COUNT_LAUNCH(1);
     }
     if (do_h && e->ms > 0) {
-        k_init_uniform<<<kNumSMs * 8, 256, 0, e->st>>>(e->H, e->c0 * r, e->ms * r,
-                                                     stream_key(e->p.seed, 1), scale);
+        k_init_uniform_cols<<<kNumSMs * 8, 256, 0, e->st>>>(e->H, e->ms, r, e->map,
+                                                          stream_key(e->p.seed, 1), scale);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
     }
@@ -549,6 +560,8 @@ int dnpeff_create(const dnpeff_params* params, int device, void* stream, dnpeff_
     if (params->rank <= 0) return fail(DNPEFF_ERR_INVALID, "rank must be positive");
     if (params->n_shards <= 0 || params->shard_index < 0 || params->shard_index >= params->n_shards)
         return fail(DNPEFF_ERR_INVALID, "shard_index/n_shards out of range");
+    if (params->shard_mode != DNPEFF_SHARD_CONTIGUOUS && params->shard_mode != DNPEFF_SHARD_CYCLIC)
+        return fail(DNPEFF_ERR_INVALID, "unknown shard_mode %d", (int)params->shard_mode);
     int ndev = 0;
     DN_CUDA(cudaGetDeviceCount(&ndev));
     if (device < 0 || device >= ndev)
@@ -655,6 +668,22 @@ int dnpeff_get_new_to_og(dnpeff_engine* e, int32_t* out) {
         DN_CUDA(cudaMemcpyAsync(out, e->new_to_og, sizeof(int32_t) * (size_t)e->m_kept, cudaMemcpyDeviceToHost, e->st));
         DN_CUDA(cudaStreamSynchronize(e->st));
     }
+    return DNPEFF_OK;
+}
+
+int dnpeff_get_shard_columns(dnpeff_engine* e, int32_t* kept_ids, int32_t* original_ids) {
+    DN_TRY(check_ready(e, false));
+    DeviceGuard g(e->device);
+    if (e->ms <= 0) return DNPEFF_OK;
+    DevBuf<int32_t> a, b;
+    DN_TRY(a.alloc((size_t)e->ms));
+    DN_TRY(b.alloc((size_t)e->ms));
+    k_shard_columns<<<(unsigned)ceil_div(e->ms, 256), 256, 0, e->st>>>(e->new_to_og, e->map, a.p, b.p);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(1);
+    if (kept_ids) DN_CUDA(cudaMemcpyAsync(kept_ids, a.p, sizeof(int32_t) * (size_t)e->ms, cudaMemcpyDeviceToHost, e->st));
+    if (original_ids) DN_CUDA(cudaMemcpyAsync(original_ids, b.p, sizeof(int32_t) * (size_t)e->ms, cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
     return DNPEFF_OK;
 }
 

@@ -9,6 +9,25 @@ namespace dnpeff {
 
 enum : int { kErrColRange = 1, kErrDuplicate = 2, kErrRowPtr = 4 };
 
+// Which kept columns an engine owns, and their local numbering.
+//   contiguous: [c0, c0+w), local = c - c0  -- the reference's equal-width split
+//               (src/util/matrix_util.h:10-20)
+//   cyclic:     c % stride == offset, local = c / stride -- spreads popular
+//               columns evenly over the engines (the equal-width split puts every
+//               popular column of a popularity-ordered feature axis on engine 0)
+struct ShardMap {
+    int64_t c0, w;
+    int32_t stride, offset;
+    int32_t cyclic;
+    __host__ __device__ bool owns(int64_t c) const {
+        return cyclic ? (c >= 0 && (c % stride) == offset) : (c >= c0 && c < c0 + w);
+    }
+    __host__ __device__ int64_t local(int64_t c) const { return cyclic ? c / stride : c - c0; }
+    __host__ __device__ int64_t global(int64_t j) const {
+        return cyclic ? j * stride + offset : c0 + j;
+    }
+};
+
 // Row i of the input owns [rowptr[i], rowptr[i+1]) or, with rowptr == NULL,
 // [i*k, (i+1)*k): the implicit offsets of a D-PEF file (src/io/pef_fisher_h5.h:175-177).
 __device__ __forceinline__ void row_range(const int64_t* rowptr, int64_t k, int64_t row,
@@ -106,7 +125,7 @@ __global__ void k_build_maps(const int32_t* __restrict__ flags, const int64_t* _
 // with the pruning test (src/util/sparse_util.h:139).  One block per row.
 __global__ void k_row_counts(const int32_t* __restrict__ colind, const int64_t* __restrict__ rowptr,
                              int64_t k, int64_t n_rows, const int32_t* __restrict__ og_to_new,
-                             int64_t c0, int64_t w, int32_t* __restrict__ row_count,
+                             ShardMap map, int32_t* __restrict__ row_count,
                              int* __restrict__ err) {
     __shared__ int ws[32];
     for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
@@ -116,7 +135,7 @@ __global__ void k_row_counts(const int32_t* __restrict__ colind, const int64_t* 
         int cnt = 0;
         for (int64_t p = b + threadIdx.x; p < e; p += blockDim.x) {
             int64_t c = og_to_new[__ldcs(colind + p)];
-            cnt += (c >= c0 && c < c0 + w) ? 1 : 0;
+            cnt += map.owns(c) ? 1 : 0;
         }
         cnt = warp_sum_i(cnt);
         __syncthreads();
@@ -137,7 +156,7 @@ __global__ void k_row_counts(const int32_t* __restrict__ colind, const int64_t* 
 __global__ void k_extract_shard(const float* __restrict__ vals, const int32_t* __restrict__ colind,
                                 const int64_t* __restrict__ rowptr, int64_t k, int64_t n_rows,
                                 const float* __restrict__ norms,
-                                const int32_t* __restrict__ og_to_new, int64_t c0, int64_t w,
+                                const int32_t* __restrict__ og_to_new, ShardMap map,
                                 const int64_t* __restrict__ out_rowptr, float* __restrict__ out_vals,
                                 int32_t* __restrict__ out_colind) {
     __shared__ int wtot[8];
@@ -155,7 +174,7 @@ __global__ void k_extract_shard(const float* __restrict__ vals, const int32_t* _
             float v = 0.f;
             if (p < e) {
                 c = og_to_new[__ldcs(colind + p)];
-                keep = (c >= c0 && c < c0 + w);
+                keep = map.owns(c);
                 v = __ldcs(vals + p);
             }
             unsigned bal = __ballot_sync(0xffffffffu, keep);
@@ -170,7 +189,7 @@ __global__ void k_extract_shard(const float* __restrict__ vals, const int32_t* _
             }
             if (keep) {
                 int64_t q = run + before + __popc(bal & ((1u << lane) - 1u));
-                out_colind[q] = (int32_t)(c - c0);
+                out_colind[q] = (int32_t)map.local(c);
                 out_vals[q] = norms ? v / denom : v;
             }
             run += total;
@@ -185,14 +204,14 @@ __global__ void k_max_rowlen(const int64_t* __restrict__ rowptr, int64_t n_rows,
     if (i < n_rows) atomicMax(out, (unsigned long long)(rowptr[i + 1] - rowptr[i]));
 }
 
-// cnt_s[j] = counts[new_to_og[c0 + j]]: every stored entry of a kept column
+// cnt_s[j] = counts[new_to_og[global(j)]]: every stored entry of a kept column
 // survives, so the pruning counts are also the shard's column lengths.
 __global__ void k_gather_counts(const int32_t* __restrict__ counts,
-                                const int32_t* __restrict__ new_to_og, int64_t c0, int64_t w,
+                                const int32_t* __restrict__ new_to_og, ShardMap map,
                                 int32_t* __restrict__ cnt_s) {
     int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j < w) cnt_s[j] = counts[new_to_og[c0 + j]];
-    else if (j == w) cnt_s[j] = 0;
+    if (j < map.w) cnt_s[j] = counts[new_to_og[map.global(j)]];
+    else if (j == map.w) cnt_s[j] = 0;
 }
 
 // ---- CSC build --------------------------------------------------------------
@@ -296,6 +315,29 @@ __global__ void k_init_uniform(float* __restrict__ out, int64_t first, int64_t c
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
         out[i] = uniform01_from_key(key, (uint64_t)(first + i)) * scale;
+}
+
+// H[j, t] = scale * U(0,1] at global index (global column of j) * r + t, so every
+// sharding of the feature axis starts from the same matrix.
+__global__ void k_init_uniform_cols(float* __restrict__ out, int64_t n_local_cols, int r,
+                                    ShardMap map, uint64_t key, float scale) {
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t count = n_local_cols * r;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+        int64_t j = i / r;
+        int t = (int)(i - j * r);
+        out[i] = uniform01_from_key(key, (uint64_t)(map.global(j) * r + t)) * scale;
+    }
+}
+
+// out[j] = original (dense_fisher_size) id of local column j.
+__global__ void k_shard_columns(const int32_t* __restrict__ new_to_og, ShardMap map,
+                                int32_t* __restrict__ kept_ids, int32_t* __restrict__ og_ids) {
+    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= map.w) return;
+    int64_t g = map.global(j);
+    if (kept_ids) kept_ids[j] = (int32_t)g;
+    if (og_ids) og_ids[j] = new_to_og[g];
 }
 
 // out[c, r] = in[r, c] for in of shape [rows, cols] (row-major both).  Used to

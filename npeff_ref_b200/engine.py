@@ -35,11 +35,13 @@ def _ptr(a):
 
 
 class MuNmf:
-    def __init__(self, params, device=0, shard_index=0, n_shards=1, stream=None):
+    CONTIGUOUS, CYCLIC = 0, 1
+
+    def __init__(self, params, device=0, shard_index=0, n_shards=1, stream=None, shard_mode=0):
         self.params = params
         self._h = C.c_void_p()
         p = Params(int(params.rank), float(params.eps), int(params.seed),
-                   float(params.init_scale), int(shard_index), int(n_shards))
+                   float(params.init_scale), int(shard_index), int(n_shards), int(shard_mode))
         check(lib().dnpeff_create(C.byref(p), int(device), C.c_void_p(stream or 0),
                                   C.byref(self._h)))
         self.device = device
@@ -97,6 +99,14 @@ class MuNmf:
         out = np.empty(max(self.shape[1], 1), dtype=np.int32)
         check(lib().dnpeff_get_new_to_og(self._h, _ptr(out)))
         return out[:self.shape[1]]
+
+    def shard_columns(self):
+        """(kept_ids, original_ids) of this shard's local columns."""
+        ms = self.shape[3]
+        a = np.empty(max(ms, 1), dtype=np.int32)
+        b = np.empty(max(ms, 1), dtype=np.int32)
+        check(lib().dnpeff_get_shard_columns(self._h, _ptr(a), _ptr(b)))
+        return a[:ms], b[:ms]
 
     def export_shard_csr(self):
         n, _, _, _, nnz = self.shape

@@ -37,10 +37,10 @@ def test_abi_version():
 
 def test_bad_params_rejected_without_touching_a_device():
     h = C.c_void_p()
-    p = Params(0, 1e-8, 1, 0.0, 0, 1)
+    p = Params(0, 1e-8, 1, 0.0, 0, 1, 0)
     assert lib().dnpeff_create(C.byref(p), 0, None, C.byref(h)) == -1
     assert b"rank" in lib().dnpeff_last_error()
-    p = Params(4, 1e-8, 1, 0.0, 2, 2)
+    p = Params(4, 1e-8, 1, 0.0, 2, 2, 0)
     assert lib().dnpeff_create(C.byref(p), 0, None, C.byref(h)) == -1
 
 

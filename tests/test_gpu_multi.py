@@ -20,7 +20,7 @@ def _n_gpus():
         return 0
 
 
-def _worker(rank, world, uid, out_dir):
+def _worker(rank, world, uid, out_dir, mode):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from npeff_ref_b200 import MuNmf, MuNmfParams
@@ -28,19 +28,20 @@ def _worker(rank, world, uid, out_dir):
     P = PROBLEM
     vals, idx, norms = make_problem(P["n"], P["m"], P["k"], seed=P["seed"])
     with MuNmf(MuNmfParams(rank=P["r"], eps=P["eps"], seed=3, init_scale=P["scale"]), device=rank,
-               shard_index=rank, n_shards=world) as eng:
+               shard_index=rank, n_shards=world, shard_mode=mode) as eng:
         eng.set_csr(P["n"], P["m"], vals, idx, None, P["k"], norms, 1)
         eng.init_comm(uid)
         eng.init_factors()
         eng.run(P["iters"], log_every=0)
         loss = eng.compute_uncached_loss()
         np.savez(os.path.join(out_dir, "rank%d.npz" % rank), W=eng.load_w_to_host(),
-                 H=eng.load_h_to_host(), loss=loss, c0=eng.shape[2])
+                 H=eng.load_h_to_host(), loss=loss, cols=eng.shard_columns()[0])
 
 
 @pytest.mark.skipif(_n_gpus() < 2, reason="needs at least 2 GPUs")
+@pytest.mark.parametrize("mode", [0, 1], ids=["contiguous", "cyclic"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_nccl_sharded_run_matches_oracle(tmp_path, world):
+def test_nccl_sharded_run_matches_oracle(tmp_path, world, mode):
     if _n_gpus() < world:
         pytest.skip("needs %d GPUs" % world)
     import torch.multiprocessing as mp
@@ -48,7 +49,7 @@ def test_nccl_sharded_run_matches_oracle(tmp_path, world):
     from oracle import oracle as O
     from helpers import make_problem, oracle_preprocess, rel_fro
     uid = MuNmf.make_unique_id()
-    mp.spawn(_worker, args=(world, uid, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, uid, str(tmp_path), mode), nprocs=world, join=True)
     parts = [np.load(os.path.join(str(tmp_path), "rank%d.npz" % r)) for r in range(world)]
     P = PROBLEM
     vals, idx, norms = make_problem(P["n"], P["m"], P["k"], seed=P["seed"])
@@ -56,7 +57,9 @@ def test_nccl_sharded_run_matches_oracle(tmp_path, world):
     mk = len(n2o)
     W0, H0 = O.init_factors(P["n"], mk, P["r"], 3, P["scale"])
     W, H, ls = O.run(v, c, rp, mk, W0, H0, P["iters"], P["eps"], losses=True)
-    Hg = np.concatenate([p["H"] for p in sorted(parts, key=lambda p: int(p["c0"]))], axis=1)
+    Hg = np.empty_like(H)
+    for p in parts:
+        Hg[:, p["cols"]] = p["H"]
     for p in parts:                      # W is replicated and identical on every rank
         assert np.array_equal(p["W"], parts[0]["W"])
         assert abs(float(p["loss"]) - ls[-1]) < 1e-5 * ls[-1]

@@ -150,6 +150,33 @@ def test_loader_bit_exact(torch_cuda, min_count, n_shards):
             assert abs(eng.a_sq_norm() - float((sv.astype(np.float64) ** 2).sum())) < 1e-9 * max(nnz, 1)
 
 
+def test_loader_cyclic_sharding_bit_exact(torch_cuda):
+    """Cyclic sharding: engine d owns kept columns d, d+G, ...; same entries, same order."""
+    from npeff_ref_b200 import MuNmfParams, MuNmf
+    n, m, k, G = 90, 1500, 60, 3
+    vals, idx, norms = make_problem(n, m, k, seed=8)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m, 2)
+    mk = len(n2o)
+    rows = np.repeat(np.arange(n), np.diff(rp))
+    seen = np.zeros(mk, dtype=bool)
+    for d in range(G):
+        with _engine(MuNmfParams(rank=8, seed=4, init_scale=0.5), shard_index=d, n_shards=G,
+                     shard_mode=MuNmf.CYCLIC) as eng:
+            eng.set_csr(n, m, vals, idx, None, k, norms, 2)
+            kept_ids, og_ids = eng.shard_columns()
+            assert np.array_equal(kept_ids, np.arange(d, mk, G))
+            assert np.array_equal(og_ids, n2o[kept_ids])
+            seen[kept_ids] = True
+            sel = (c % G) == d
+            gv, gc, grp = eng.export_shard_csr()
+            assert np.array_equal(gc, c[sel] // G) and np.array_equal(gv, v[sel])
+            assert np.array_equal(np.diff(grp), np.bincount(rows[sel], minlength=n))
+            eng.init_factors()
+            _, H0 = O.init_factors(n, mk, 8, 4, 0.5)
+            assert np.array_equal(eng.load_h_to_host(), H0[:, kept_ids])
+    assert seen.all()
+
+
 def test_loader_ragged_rows_and_empty_rows(torch_cuda):
     from npeff_ref_b200 import MuNmfParams
     rng = np.random.default_rng(5)
