@@ -122,6 +122,41 @@ int dnpeff_a_sq_norm(dnpeff_engine* eng, double* out);
 /* sum of the shard's stored values (for the Uniform*sqrt(mean(A)/r) initial scale). */
 int dnpeff_a_sum(dnpeff_engine* eng, double* out);
 
+/* ---- files ------------------------------------------------------------------
+ * The D-PEF input file (written by npeff/fishers/d_pefs_computer.py:235-251):
+ *   data/fisher/values  float32 [n, k],  data/fisher/indices int32 [n, k],
+ *   attribute dense_fisher_size on group data/fisher,
+ *   data/dense_fisher_norms float32 [n].
+ * dnpeff_pef_hdf5_info replaces the dimension probe of
+ * Pef::pefRequiresInt64Indices (src/io/pef_fisher_h5.h:57-90);
+ * dnpeff_read_pef_hdf5 / dnpeff_load_pef_hdf5 replace PefSparseFishers::read
+ * (:107-226): n_examples / n_fisher_values <= 0 mean "all", otherwise the leading
+ * rows / leading values per row are taken (--n_examples, --n_fisher_values).
+ * dnpeff_load_pef_hdf5 = read + dnpeff_set_csr.  Files are read and written by a
+ * built-in HDF5 codec (contiguous, uncompressed datasets only). */
+int dnpeff_pef_hdf5_info(const char* path, int64_t* n_examples, int64_t* n_values_per_example,
+                         int64_t* dense_fisher_size);
+int dnpeff_read_pef_hdf5(const char* path, int64_t n_examples, int64_t n_fisher_values, float* vals,
+                         int32_t* indices, float* norms);
+int dnpeff_load_pef_hdf5(dnpeff_engine* eng, const char* path, int64_t n_examples,
+                         int64_t n_fisher_values, int32_t min_values_per_parameter);
+/* NmfDecomposition<IndT>::save (src/io/nmf_decomp_h5.h:38-89): data/W [n, r],
+ * data/H [r, n_kept], data/reduce_kept_indices [n_kept] (int32) with attribute
+ * full_dense_size of shape {1}; the file npeff/decomp/decomps.py:55-71 loads. */
+int dnpeff_save_decomposition_hdf5(const char* path, const float* W, const float* H,
+                                   const int32_t* reduce_kept_indices, int64_t n_examples,
+                                   int32_t rank, int64_t n_kept, int64_t full_dense_size);
+/* NmfDecomposition<IndT>::read (src/io/nmf_decomp_h5.h:100-126), used for
+ * --initial_W_path / --initial_H_path.  Any output may be NULL. */
+int dnpeff_decomposition_hdf5_info(const char* path, int64_t* n_examples, int32_t* rank,
+                                   int64_t* n_kept, int64_t* full_dense_size);
+int dnpeff_read_decomposition_hdf5(const char* path, float* W, float* H, int32_t* reduce_kept_indices);
+/* Shape/type of any dataset, and its leading rows x cols block as float64
+ * (src/util/h5_util.h helpers). */
+int dnpeff_hdf5_dataset_info(const char* path, const char* dataset, int32_t* rank, int64_t dims[4],
+                             int32_t* is_float, int32_t* type_size);
+int dnpeff_hdf5_read_f64(const char* path, const char* dataset, int64_t rows, int64_t cols, double* out);
+
 /* ---- factors --------------------------------------------------------------
  * initializeW / initializeH / broadcastInitializedW (…device_contexts1.h:197-233,
  * multi_mu_dense_factors_nmf1.h:131-135,358-375).  W: [n_rows, rank] row-major

@@ -24,6 +24,14 @@ int dnpeff_synth_pef_device(int64_t n_rows, int64_t n_cols, int64_t k_per_row, d
                             double sigma, uint64_t seed, float* d_vals, int32_t* d_idx,
                             float* d_norms, void* stream);
 
+/* Writes host arrays as a D-PEF file in the layout of
+ * npeff/fishers/d_pefs_computer.py:235-251 (what dnpeff_load_pef_hdf5 and the
+ * reference's PefSparseFishers::read consume).  The reference has no C++ writer
+ * for this file: it is produced by its TensorFlow pipeline. */
+int dnpeff_write_pef_hdf5(const char* path, int64_t n_examples, int64_t n_values_per_example,
+                          const float* vals, const int32_t* indices, const float* norms,
+                          int64_t dense_fisher_size);
+
 #ifdef __cplusplus
 }
 #endif

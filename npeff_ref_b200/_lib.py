@@ -63,6 +63,17 @@ SIGNATURES = {
     "dnpeff_op_spmm": (C.c_int, [_P, _P, _P, _I64, _P, _I32, _P, _P]),
     "dnpeff_op_gram": (C.c_int, [_P, _I64, _I32, _P, _P]),
     "dnpeff_op_mu_update": (C.c_int, [_P, _P, _P, _I64, _I32, C.c_float, _P]),
+    "dnpeff_pef_hdf5_info": (C.c_int, [C.c_char_p] + [C.POINTER(_I64)] * 3),
+    "dnpeff_read_pef_hdf5": (C.c_int, [C.c_char_p, _I64, _I64, _P, _P, _P]),
+    "dnpeff_load_pef_hdf5": (C.c_int, [_P, C.c_char_p, _I64, _I64, _I32]),
+    "dnpeff_save_decomposition_hdf5": (C.c_int, [C.c_char_p, _P, _P, _P, _I64, _I32, _I64, _I64]),
+    "dnpeff_decomposition_hdf5_info": (C.c_int, [C.c_char_p, C.POINTER(_I64), C.POINTER(_I32),
+                                                 C.POINTER(_I64), C.POINTER(_I64)]),
+    "dnpeff_read_decomposition_hdf5": (C.c_int, [C.c_char_p, _P, _P, _P]),
+    "dnpeff_hdf5_dataset_info": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(_I32), C.POINTER(_I64),
+                                           C.POINTER(_I32), C.POINTER(_I32)]),
+    "dnpeff_hdf5_read_f64": (C.c_int, [C.c_char_p, C.c_char_p, _I64, _I64, _P]),
+    "dnpeff_write_pef_hdf5": (C.c_int, [C.c_char_p, _I64, _I64, _P, _P, _P, _I64]),
     "dnpeff_op_gram_noalloc": (C.c_int, [_P, _I64, _I32, _P, _P]),
     "dnpeff_synth_pef_device": (C.c_int, [_I64, _I64, _I64, C.c_double, C.c_double, C.c_uint64,
                                           _P, _P, _P, _P]),

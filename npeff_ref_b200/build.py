@@ -11,6 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdnpeff.so")
+CLI = os.path.join(HERE, "bin", "run_nmf_on_pefs")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -36,8 +37,19 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in _deps())
 
 
+def build_cli():
+    """The `run_nmf_on_pefs` executable: plain C++ over the C ABI."""
+    os.makedirs(os.path.dirname(CLI), exist_ok=True)
+    cmd = ["g++", "-O2", "-std=c++17", "-o", CLI, os.path.join(CSRC, "run_nmf_on_pefs.cpp"),
+           "-L" + HERE, "-ldnpeff", "-Wl,-rpath,$ORIGIN/..", "-lpthread"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return CLI
+
+
 def build(force=False, verbose=False):
-    if not force and not needs_build():
+    if not force and not needs_build() and os.path.exists(CLI):
         return LIB
     cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
         ["-o", LIB] + _sources() + ["-ldl"]
@@ -46,6 +58,7 @@ def build(force=False, verbose=False):
         sys.stderr.write(res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    build_cli()
     return LIB
 
 

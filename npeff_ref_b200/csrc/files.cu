@@ -1,0 +1,220 @@
+// File entry points of the C ABI: D-PEF input (src/io/pef_fisher_h5.h:57-226) and
+// decomposition output/input (src/io/nmf_decomp_h5.h:38-126) through the built-in
+// HDF5 codec.  Host code only.
+#include <vector>
+
+#include "../../include/dnpeff_synth.h"
+#include "common.cuh"
+#include "h5lite.hpp"
+
+using namespace dnpeff;
+
+namespace {
+
+struct PefShape {
+    int64_t n = 0, k = 0, dense = 0;
+};
+
+// Dimensions of data/fisher/values plus the dense_fisher_size attribute of
+// data/fisher (pef_fisher_h5.h:117-154; the reference insists on a 4-byte
+// attribute, here any integer width is accepted).
+PefShape pef_shape(h5lite::Reader& rd) {
+    h5lite::ObjectInfo v = rd.dataset("data/fisher/values");
+    if (v.space.dims.size() != 2) throw h5lite::Error("data/fisher/values must have rank 2");
+    h5lite::ObjectInfo i = rd.dataset("data/fisher/indices");
+    if (i.space.dims != v.space.dims) throw h5lite::Error("data/fisher/indices and values differ in shape");
+    PefShape s;
+    s.n = (int64_t)v.space.dims[0];
+    s.k = (int64_t)v.space.dims[1];
+    s.dense = rd.attr_int(rd.object(rd.find("data/fisher")), "dense_fisher_size");
+    return s;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dnpeff_pef_hdf5_info(const char* path, int64_t* n_examples, int64_t* n_values_per_example,
+                         int64_t* dense_fisher_size) {
+    if (!path) return fail(DNPEFF_ERR_INVALID, "null path");
+    try {
+        h5lite::Reader rd(path);
+        PefShape s = pef_shape(rd);
+        if (n_examples) *n_examples = s.n;
+        if (n_values_per_example) *n_values_per_example = s.k;
+        if (dense_fisher_size) *dense_fisher_size = s.dense;
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_read_pef_hdf5(const char* path, int64_t n_examples, int64_t n_fisher_values, float* vals,
+                         int32_t* indices, float* norms) {
+    if (!path) return fail(DNPEFF_ERR_INVALID, "null path");
+    try {
+        h5lite::Reader rd(path);
+        PefShape s = pef_shape(rd);
+        int64_t n = n_examples > 0 ? n_examples : s.n, k = n_fisher_values > 0 ? n_fisher_values : s.k;
+        if (n > s.n || k > s.k) return fail(DNPEFF_ERR_INVALID, "requested %ld x %ld of a %ld x %ld file",
+                                            (long)n, (long)k, (long)s.n, (long)s.k);
+        if (vals) rd.read_leading(rd.dataset("data/fisher/values"), n, k, h5lite::DType::f32(), vals);
+        if (indices) rd.read_leading(rd.dataset("data/fisher/indices"), n, k, h5lite::DType::i32(), indices);
+        if (norms) rd.read_leading(rd.dataset("data/dense_fisher_norms"), n, 1, h5lite::DType::f32(), norms);
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_load_pef_hdf5(dnpeff_engine* eng, const char* path, int64_t n_examples,
+                         int64_t n_fisher_values, int32_t min_values_per_parameter) {
+    if (!eng || !path) return fail(DNPEFF_ERR_INVALID, "null argument");
+    int64_t n = 0, k = 0, dense = 0;
+    DN_TRY(dnpeff_pef_hdf5_info(path, &n, &k, &dense));
+    if (n_examples > 0) {
+        if (n_examples > n) return fail(DNPEFF_ERR_INVALID, "--n_examples exceeds the file's %ld rows", (long)n);
+        n = n_examples;
+    }
+    if (n_fisher_values > 0) {
+        if (n_fisher_values > k) return fail(DNPEFF_ERR_INVALID, "--n_fisher_values exceeds the file's %ld", (long)k);
+        k = n_fisher_values;
+    }
+    float* vals = nullptr;
+    int32_t* idx = nullptr;
+    float* norms = nullptr;
+    size_t nnz = (size_t)n * (size_t)k;
+    // pinned staging so the upload runs at full PCIe rate
+    if (cudaMallocHost((void**)&vals, sizeof(float) * (nnz ? nnz : 1)) != cudaSuccess ||
+        cudaMallocHost((void**)&idx, sizeof(int32_t) * (nnz ? nnz : 1)) != cudaSuccess ||
+        cudaMallocHost((void**)&norms, sizeof(float) * (size_t)(n ? n : 1)) != cudaSuccess) {
+        cudaFreeHost(vals); cudaFreeHost(idx); cudaFreeHost(norms);
+        return fail(DNPEFF_ERR_CUDA, "pinned host allocation for the D-PEF file failed");
+    }
+    int s = dnpeff_read_pef_hdf5(path, n, k, vals, idx, norms);
+    if (s == DNPEFF_OK)
+        s = dnpeff_set_csr(eng, n, dense, k, nullptr, vals, idx, norms, min_values_per_parameter);
+    cudaFreeHost(vals); cudaFreeHost(idx); cudaFreeHost(norms);
+    return s;
+}
+
+int dnpeff_save_decomposition_hdf5(const char* path, const float* W, const float* H,
+                                   const int32_t* reduce_kept_indices, int64_t n_examples,
+                                   int32_t rank, int64_t n_kept, int64_t full_dense_size) {
+    if (!path || !W || !H || (!reduce_kept_indices && n_kept > 0)) return fail(DNPEFF_ERR_INVALID, "null argument");
+    try {
+        h5lite::Writer w(path);
+        w.add_group("data");
+        w.add_dataset("data/W", h5lite::DType::f32(), {(uint64_t)n_examples, (uint64_t)rank}, W);
+        w.add_dataset("data/H", h5lite::DType::f32(), {(uint64_t)rank, (uint64_t)n_kept}, H);
+        w.add_dataset("data/reduce_kept_indices", h5lite::DType::i32(), {(uint64_t)n_kept}, reduce_kept_indices);
+        int32_t fds = (int32_t)full_dense_size;
+        w.add_attr("data/reduce_kept_indices", "full_dense_size", h5lite::DType::i32(), {1}, &fds);
+        w.finish();
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_decomposition_hdf5_info(const char* path, int64_t* n_examples, int32_t* rank,
+                                   int64_t* n_kept, int64_t* full_dense_size) {
+    if (!path) return fail(DNPEFF_ERR_INVALID, "null path");
+    try {
+        h5lite::Reader rd(path);
+        h5lite::ObjectInfo W = rd.dataset("data/W"), H = rd.dataset("data/H");
+        h5lite::ObjectInfo K = rd.dataset("data/reduce_kept_indices");
+        if (W.space.dims.size() != 2 || H.space.dims.size() != 2 || W.space.dims[1] != H.space.dims[0])
+            return fail(DNPEFF_ERR_IO, "data/W and data/H do not form a decomposition");
+        if (n_examples) *n_examples = (int64_t)W.space.dims[0];
+        if (rank) *rank = (int32_t)W.space.dims[1];
+        if (n_kept) *n_kept = (int64_t)H.space.dims[1];
+        if (full_dense_size) *full_dense_size = rd.attr_int(K, "full_dense_size");
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_read_decomposition_hdf5(const char* path, float* W, float* H, int32_t* reduce_kept_indices) {
+    if (!path) return fail(DNPEFF_ERR_INVALID, "null path");
+    try {
+        h5lite::Reader rd(path);
+        if (W) {
+            h5lite::ObjectInfo o = rd.dataset("data/W");
+            rd.read_leading(o, o.space.dims[0], o.space.dims[1], h5lite::DType::f32(), W);
+        }
+        if (H) {
+            h5lite::ObjectInfo o = rd.dataset("data/H");
+            rd.read_leading(o, o.space.dims[0], o.space.dims[1], h5lite::DType::f32(), H);
+        }
+        if (reduce_kept_indices) {
+            h5lite::ObjectInfo o = rd.dataset("data/reduce_kept_indices");
+            rd.read_leading(o, o.space.dims[0], 1, h5lite::DType::i32(), reduce_kept_indices);
+        }
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+// Generic probe used by the tests: shape and type of any dataset.
+int dnpeff_hdf5_dataset_info(const char* path, const char* dataset, int32_t* rank, int64_t dims[4],
+                             int32_t* is_float, int32_t* type_size) {
+    if (!path || !dataset) return fail(DNPEFF_ERR_INVALID, "null argument");
+    try {
+        h5lite::Reader rd(path);
+        h5lite::ObjectInfo o = rd.dataset(dataset);
+        if (o.space.dims.size() > 4) return fail(DNPEFF_ERR_UNSUPPORTED, "rank > 4");
+        if (rank) *rank = (int32_t)o.space.dims.size();
+        for (size_t i = 0; i < o.space.dims.size() && dims; i++) dims[i] = (int64_t)o.space.dims[i];
+        if (is_float) *is_float = o.type.cls == h5lite::TypeClass::Float;
+        if (type_size) *type_size = o.type.size;
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+// Reads the leading rows x cols block of a rank <= 2 dataset as float64.
+int dnpeff_hdf5_read_f64(const char* path, const char* dataset, int64_t rows, int64_t cols, double* out) {
+    if (!path || !dataset || !out) return fail(DNPEFF_ERR_INVALID, "null argument");
+    try {
+        h5lite::Reader rd(path);
+        h5lite::ObjectInfo o = rd.dataset(dataset);
+        h5lite::DType f64 = {h5lite::TypeClass::Float, 8, true, false};
+        rd.read_leading(o, (uint64_t)rows, (uint64_t)cols, f64, out);
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+// Writes a D-PEF file with the layout of npeff/fishers/d_pefs_computer.py:235-251
+// (data/fisher/{values,indices} + attribute dense_fisher_size, data/dense_fisher_norms).
+int dnpeff_write_pef_hdf5(const char* path, int64_t n_examples, int64_t n_values_per_example,
+                          const float* vals, const int32_t* indices, const float* norms,
+                          int64_t dense_fisher_size) {
+    if (!path || !vals || !indices || !norms) return fail(DNPEFF_ERR_INVALID, "null argument");
+    try {
+        h5lite::Writer w(path);
+        w.add_group("data");
+        w.add_group("data/fisher");
+        int64_t dfs64 = dense_fisher_size;
+        int32_t dfs32 = (int32_t)dense_fisher_size;
+        // the reference reader demands a 4-byte attribute (pef_fisher_h5.h:145-154)
+        if (dense_fisher_size <= INT32_MAX) w.add_attr("data/fisher", "dense_fisher_size", h5lite::DType::i32(), {}, &dfs32);
+        else w.add_attr("data/fisher", "dense_fisher_size", h5lite::DType::i64(), {}, &dfs64);
+        w.add_dataset("data/fisher/values", h5lite::DType::f32(),
+                      {(uint64_t)n_examples, (uint64_t)n_values_per_example}, vals);
+        w.add_dataset("data/fisher/indices", h5lite::DType::i32(),
+                      {(uint64_t)n_examples, (uint64_t)n_values_per_example}, indices);
+        w.add_dataset("data/dense_fisher_norms", h5lite::DType::f32(), {(uint64_t)n_examples}, norms);
+        w.finish();
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+}  // extern "C"

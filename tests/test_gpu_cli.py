@@ -1,0 +1,101 @@
+"""The `run_nmf_on_pefs` drop-in executable end to end on a GPU: D-PEF file in,
+decomposition file out, same flags and progress lines as the reference
+(cc/cuda_d_npeff/mains/run_nmf_on_pefs.cu), checked against the CPU oracle."""
+import ctypes as C
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from helpers import rel_fro, make_problem, oracle_preprocess
+from npeff_ref_b200._lib import lib, check
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CLI = os.path.join(ROOT, "npeff_ref_b200", "bin", "run_nmf_on_pefs")
+SEED = 43190432042  # compiled into the reference executable (run_nmf_on_pefs.cu:190)
+
+
+def _write_pef(path, vals, idx, norms, dense):
+    n, k = vals.shape
+    check(lib().dnpeff_write_pef_hdf5(path.encode(), n, k, C.c_void_p(vals.ctypes.data),
+                                      C.c_void_p(idx.ctypes.data), C.c_void_p(norms.ctypes.data), dense))
+
+
+def _read_decomp(path):
+    a, b, c, d = C.c_int64(0), C.c_int32(0), C.c_int64(0), C.c_int64(0)
+    check(lib().dnpeff_decomposition_hdf5_info(path.encode(), C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+    W = np.empty((a.value, b.value), np.float32)
+    H = np.empty((b.value, c.value), np.float32)
+    kept = np.empty(c.value, np.int32)
+    check(lib().dnpeff_read_decomposition_hdf5(path.encode(), C.c_void_p(W.ctypes.data),
+                                               C.c_void_p(H.ctypes.data), C.c_void_p(kept.ctypes.data)))
+    return W, H, kept, d.value
+
+
+def _run(*flags):
+    res = subprocess.run([CLI] + list(flags), capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+    return res.stdout
+
+
+def test_cli_matches_oracle_and_writes_reference_layout(tmp_path):
+    n, m, k, r, iters = 120, 4000, 90, 16, 30
+    vals, idx, norms = make_problem(n, m, k, seed=61)
+    pef, out = str(tmp_path / "pef.h5"), str(tmp_path / "nmf.h5")
+    _write_pef(pef, vals, idx, norms, m)
+    stdout = _run("--per_example_fishers=" + pef, "--output_path=" + out, "--nmf_n_components=%d" % r,
+                  "--nmf_max_iter=%d" % iters, "--min_values_per_parameter=2", "--some_unknown_flag=1")
+    W, H, kept, dense = _read_decomp(out)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m, 2)
+    mk = len(n2o)
+    assert dense == m and np.array_equal(kept, n2o)
+    assert W.shape == (n, r) and H.shape == (r, mk)
+    W0, H0 = O.init_factors(n, mk, r, SEED, 1.0)           # unscaled U(0,1], eps 1e-8: the reference's defaults
+    Wo, Ho, ls = O.run(v, c, rp, mk, W0, H0, iters, 1e-8, losses=True)
+    assert rel_fro(W, Wo) < 1e-4 and rel_fro(H, Ho) < 1e-4
+    # "step N: <loss> [<ms> ms/step]" every 10 steps (multi_mu_dense_factors_nmf1.h:198)
+    steps = re.findall(r"^step (\d+): ([0-9.eE+-]+) \[([0-9.eE+-]+) ms/step\]$", stdout, flags=re.M)
+    assert [int(s[0]) for s in steps] == [10, 20, 30]
+    for s in steps:
+        assert abs(float(s[1]) - ls[int(s[0]) - 1]) < 1e-4 * ls[int(s[0]) - 1]   # printed with 6 digits
+
+
+def test_cli_leading_hyperslab_flags(tmp_path):
+    n, m, k, r = 80, 2000, 64, 8
+    vals, idx, norms = make_problem(n, m, k, seed=62)
+    pef, out = str(tmp_path / "pef.h5"), str(tmp_path / "nmf.h5")
+    _write_pef(pef, vals, idx, norms, m)
+    _run("--per_example_fishers=" + pef, "--output_path=" + out, "--nmf_n_components=%d" % r,
+         "--nmf_max_iter=5", "--n_examples=50", "--n_fisher_values=40", "--log_every=0")
+    W, H, kept, _ = _read_decomp(out)
+    v, c, rp, n2o = oracle_preprocess(vals[:50, :40], idx[:50, :40], norms[:50], m, 1)
+    assert np.array_equal(kept, n2o) and W.shape == (50, r)
+    W0, H0 = O.init_factors(50, len(n2o), r, SEED, 1.0)
+    Wo, Ho = O.run(v, c, rp, len(n2o), W0, H0, 5, 1e-8)
+    assert rel_fro(W, Wo) < 1e-4 and rel_fro(H, Ho) < 1e-4
+
+
+def test_cli_resume_from_initial_factor_files(tmp_path):
+    """--initial_W_path / --initial_H_path (parsed but dead in the reference,
+    run_nmf_on_pefs.cu:131-156): 10 + 10 iterations equal 20 in one go, bit for bit."""
+    n, m, k, r = 100, 3000, 80, 12
+    vals, idx, norms = make_problem(n, m, k, seed=63)
+    pef = str(tmp_path / "pef.h5")
+    _write_pef(pef, vals, idx, norms, m)
+    common = ["--per_example_fishers=" + pef, "--nmf_n_components=%d" % r, "--log_every=0", "--n_devices=1"]
+    a, b, full = str(tmp_path / "a.h5"), str(tmp_path / "b.h5"), str(tmp_path / "full.h5")
+    _run(*common, "--output_path=" + a, "--nmf_max_iter=10")
+    _run(*common, "--output_path=" + b, "--nmf_max_iter=10", "--initial_W_path=" + a, "--initial_H_path=" + a)
+    _run(*common, "--output_path=" + full, "--nmf_max_iter=20")
+    Wb, Hb, kb, _ = _read_decomp(b)
+    Wf, Hf, kf, _ = _read_decomp(full)
+    assert np.array_equal(kb, kf) and np.array_equal(Wb, Wf) and np.array_equal(Hb, Hf)
+
+
+def test_cli_missing_required_flag_aborts():
+    res = subprocess.run([CLI, "--output_path=/tmp/x.h5"], capture_output=True, text=True)
+    assert res.returncode != 0 and "Missing flag: per_example_fishers" in res.stdout
