@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <functional>
 #include <mutex>
 #include <vector>
 
@@ -110,6 +111,20 @@ struct dnpeff_engine {
     int64_t* c_colptr = nullptr;
     int32_t* new_to_og = nullptr;
 
+    // Internal column order: [n_hot popular columns][the rest], each in local-id
+    // order.  H, WA and the CSC use it; perm[jp] = local id, inv_perm[local] = jp.
+    int32_t* perm = nullptr;
+    int32_t* inv_perm = nullptr;
+    int64_t n_hot = 0;
+    BucketMap bm = {0, 1, 1, 0, 0};
+    int n_tail_blocks = 0;
+    float* b_vals = nullptr;      // rows of A with entries grouped by bucket, internal ids
+    int32_t* b_col = nullptr;
+    uint32_t* tail_off = nullptr;  // [n][n_tail_blocks + 1]
+    std::vector<int64_t> tail_nnz;  // stored entries per tail block
+    int* work_counter = nullptr;
+    int* d_err = nullptr;
+
     float* W = nullptr;
     float* H = nullptr;
     float* AHG = nullptr;  // [n*r | r*r]: A*H^T partial and H*H^T partial, one allreduce
@@ -137,7 +152,12 @@ struct dnpeff_engine {
 
 namespace {
 
+int check_kernel_status(dnpeff_engine* e);
+
 constexpr int kRedBlocks = 4 * kNumSMs;
+constexpr int kMaxHotTiles = 1024;            // tiles of popular columns per row walk
+constexpr int64_t kTailBlockBytes = 24 << 20;  // slice of H gathered per tail launch (L2-resident)
+constexpr int kMaxTailBlocks = 512;
 
 struct DeviceGuard {
     int prev = -1;
@@ -182,6 +202,10 @@ void free_matrix(dnpeff_engine* e) {
     dev_free(e->a_vals); dev_free(e->a_col); dev_free(e->a_rowptr);
     dev_free(e->c_vals); dev_free(e->c_row); dev_free(e->c_colptr);
     dev_free(e->new_to_og);
+    dev_free(e->perm); dev_free(e->inv_perm);
+    dev_free(e->b_vals); dev_free(e->b_col); dev_free(e->tail_off);
+    e->tail_nnz.clear();
+    e->n_hot = 0; e->n_tail_blocks = 0;
     dev_free(e->W); dev_free(e->H); dev_free(e->AHG); dev_free(e->WA); dev_free(e->WW);
     dev_free(e->gram_scratch);
     e->gram_scratch_floats = 0;
@@ -314,14 +338,107 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         DN_COUNT_LAUNCH(1);
     }
 
-    // 6. column offsets of the shard's CSC (the arrays are filled on first use)
-    DevBuf<int32_t> cnt_s;
+    // 6. internal column order: popular columns first (they get the tiled,
+    //    shared-memory kernels), then the rest; both parts in local-id order
+    DevBuf<int32_t> cnt_s, hot_flags, cnt_p;
+    DevBuf<int64_t> hot_pos;
     DN_TRY(cnt_s.alloc((size_t)ms + 1));
-    DN_CUDA(cudaMalloc((void**)&e->c_colptr, sizeof(int64_t) * (size_t)(ms + 1)));
     k_gather_counts<<<(unsigned)ceil_div(ms + 1, 256), 256, 0, st>>>(counts.p, e->new_to_og, map, cnt_s.p);
     DN_LAUNCH_CHECK();
     DN_COUNT_LAUNCH(1);
-    DN_TRY(scan_exclusive<int32_t>(cnt_s.p, e->c_colptr, ms + 1, st));
+    const bool fast = spmm_fast_rank(r);
+    const int tile = fast ? spmm_tile_rows(r) : 128;
+    int32_t hot_thr = (int32_t)std::max<int64_t>(2, ceil_div(n, 8));
+    if (!fast || n < 32) hot_thr = INT32_MAX;  // no hot part
+    DN_TRY(hot_flags.alloc((size_t)ms + 1));
+    DN_TRY(hot_pos.alloc((size_t)ms + 1));
+    k_hot_flags<<<(unsigned)ceil_div(ms + 1, 256), 256, 0, st>>>(cnt_s.p, ms, hot_thr, hot_flags.p);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(1);
+    DN_TRY(scan_exclusive<int32_t>(hot_flags.p, hot_pos.p, ms + 1, st));
+    int64_t n_hot = 0;
+    DN_CUDA(cudaMemcpyAsync(&n_hot, hot_pos.p + ms, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    DN_CUDA(cudaStreamSynchronize(st));
+    const int64_t max_hot = (int64_t)kMaxHotTiles * tile;
+    if (n_hot > max_hot || n_hot < 8) {
+        // too many (cap the tile loop) or too few to be worth a launch: raise the
+        // bar until the count fits, or drop the hot part
+        if (n_hot > max_hot) {
+            // keep the max_hot most popular: find the count threshold by bisection on the host
+            std::vector<int32_t> hc((size_t)ms);
+            DN_CUDA(cudaMemcpyAsync(hc.data(), cnt_s.p, sizeof(int32_t) * (size_t)ms, cudaMemcpyDeviceToHost, st));
+            DN_CUDA(cudaStreamSynchronize(st));
+            std::vector<int32_t> sorted(hc);
+            std::nth_element(sorted.begin(), sorted.begin() + (size_t)max_hot, sorted.end(), std::greater<int32_t>());
+            hot_thr = sorted[(size_t)max_hot] + 1;
+        } else {
+            hot_thr = INT32_MAX;
+        }
+        k_hot_flags<<<(unsigned)ceil_div(ms + 1, 256), 256, 0, st>>>(cnt_s.p, ms, hot_thr, hot_flags.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+        DN_TRY(scan_exclusive<int32_t>(hot_flags.p, hot_pos.p, ms + 1, st));
+        DN_CUDA(cudaMemcpyAsync(&n_hot, hot_pos.p + ms, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+        DN_CUDA(cudaStreamSynchronize(st));
+    }
+    DN_CUDA(cudaMalloc((void**)&e->perm, sizeof(int32_t) * (size_t)std::max<int64_t>(ms, 1)));
+    DN_CUDA(cudaMalloc((void**)&e->inv_perm, sizeof(int32_t) * (size_t)std::max<int64_t>(ms, 1)));
+    if (ms > 0) {
+        k_build_perm<<<(unsigned)ceil_div(ms, 256), 256, 0, st>>>(hot_flags.p, hot_pos.p, ms, n_hot, e->perm, e->inv_perm);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+    // column offsets of the CSC in internal order (the arrays are filled on first use)
+    DN_TRY(cnt_p.alloc((size_t)ms + 1));
+    DN_CUDA(cudaMalloc((void**)&e->c_colptr, sizeof(int64_t) * (size_t)(ms + 1)));
+    k_permute_counts<<<(unsigned)ceil_div(ms + 1, 256), 256, 0, st>>>(cnt_s.p, e->perm, ms, cnt_p.p);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(1);
+    DN_TRY(scan_exclusive<int32_t>(cnt_p.p, e->c_colptr, ms + 1, st));
+
+    // 6b. rows of A partitioned into buckets: hot tiles, then tail column blocks
+    //     narrow enough for their slice of H to stay in L2 while it is gathered
+    {
+        int64_t tail_cols = ms - n_hot;
+        int64_t block = std::max<int64_t>(4096, ((int64_t)kTailBlockBytes / (4 * (int64_t)r)) / 32 * 32);
+        int64_t nb = ceil_div(std::max<int64_t>(tail_cols, 1), block);
+        if (nb > kMaxTailBlocks) {
+            block = ceil_div(ceil_div(tail_cols, kMaxTailBlocks), 32) * 32;
+            nb = ceil_div(tail_cols, block);
+        }
+        if (tail_cols <= 0) nb = 0;
+        BucketMap bm;
+        bm.n_hot = n_hot;
+        bm.tile = tile;
+        bm.block = (int32_t)block;
+        bm.n_hot_tiles = (int32_t)ceil_div(n_hot, tile);
+        bm.n_buckets = bm.n_hot_tiles + (int32_t)nb;
+        e->bm = bm;
+        e->n_hot = n_hot;
+        e->n_tail_blocks = (int)nb;
+        DN_CUDA(cudaMalloc((void**)&e->b_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
+        DN_CUDA(cudaMalloc((void**)&e->b_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
+        DN_CUDA(cudaMalloc((void**)&e->tail_off, sizeof(uint32_t) * (size_t)std::max<int64_t>(n * (nb + 1), 1)));
+        if (n > 0) {
+            size_t smem = sizeof(int) * 8 * (size_t)std::max(bm.n_buckets, 1);
+            int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 16);
+            k_bucket_rows<<<(unsigned)blocks, 256, smem, st>>>(e->a_vals, e->a_col, e->a_rowptr, n, e->inv_perm,
+                                                              bm, e->b_vals, e->b_col, e->tail_off);
+            DN_LAUNCH_CHECK();
+            DN_COUNT_LAUNCH(1);
+        }
+        // stored entries per tail block (decides warp-per-row or block-per-row launches)
+        std::vector<int64_t> colptr_h;
+        e->tail_nnz.assign((size_t)nb, 0);
+        for (int64_t b = 0; b < nb; b++) {
+            int64_t lo = n_hot + b * block, hi = std::min<int64_t>(ms, lo + block);
+            int64_t v[2];
+            DN_CUDA(cudaMemcpyAsync(&v[0], e->c_colptr + lo, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+            DN_CUDA(cudaMemcpyAsync(&v[1], e->c_colptr + hi, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+            DN_CUDA(cudaStreamSynchronize(st));
+            e->tail_nnz[(size_t)b] = v[1] - v[0];
+        }
+    }
 
     // 7. |A|^2 and sum(A) of the shard
     k_sum_sumsq<<<kRedBlocks, 256, 0, st>>>(e->a_vals, nnz, e->red_partial);
@@ -345,8 +462,8 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_CUDA(cudaMalloc((void**)&e->WW, sizeof(float) * (size_t)((int64_t)r * r)));
     e->gram_scratch_floats = std::max(gram_plan(n, r).scratch_floats, gram_plan(ms, r).scratch_floats);
     DN_CUDA(cudaMalloc((void**)&e->gram_scratch, sizeof(float) * e->gram_scratch_floats));
-    DN_TRY(spmm_make_plan(e->a_rowptr, n, &e->plan_csr, st));
-    DN_TRY(spmm_make_plan(e->c_colptr, ms, &e->plan_csc, st));
+    DN_TRY(spmm_make_plan(e->a_rowptr, 0, n, &e->plan_csr, st));
+    DN_TRY(spmm_make_plan(e->c_colptr, e->n_hot, ms - e->n_hot, &e->plan_csc, st));
     e->loaded = true;
     return DNPEFF_OK;
 }
@@ -374,10 +491,10 @@ int build_csc(dnpeff_engine* e) {
         if (hmax > 0) {
             dim3 grid((unsigned)ceil_div((int64_t)hmax, 256), 64);
             for (int64_t base = 0; base < e->n; base += 64) {
-                k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->a_col, base, e->n, mask.p, err.p);
-                k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->a_col, e->a_vals, base, e->n, mask.p,
+                k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, mask.p, err.p);
+                k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, base, e->n, mask.p,
                                                   e->c_colptr, cursor.p, e->c_vals, e->c_row);
-                k_csc_advance<<<grid, 256, 0, st>>>(e->a_rowptr, e->a_col, base, e->n, mask.p, cursor.p);
+                k_csc_advance<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, mask.p, cursor.p);
                 DN_COUNT_LAUNCH(3);
             }
             DN_LAUNCH_CHECK();
@@ -406,13 +523,77 @@ int device_dot(dnpeff_engine* e, const float* a, const float* b, int64_t count, 
     return DNPEFF_OK;
 }
 
+// A*H^T: the popular columns through the tiled kernel (H tiles staged in shared
+// memory), then one launch per tail column block, each adding to AH, so that the
+// slice of H being gathered stays L2-resident.
+int spmm_ah(dnpeff_engine* e, float* AH) {
+    const int r = e->p.rank;
+    if (!spmm_fast_rank(r))
+        return spmm_dispatch(e->b_vals, e->b_col, e->a_rowptr, e->n, e->H, r, AH, e->plan_csr, e->st);
+    if (e->n <= 0) return DNPEFF_OK;
+    int accumulate = 0;
+    const int stride = e->n_tail_blocks + 1;
+    if (e->n_hot > 0) {
+        SpmmCall c;
+        c.kind = kSpmmTiled;
+        c.vals = e->b_vals; c.ind = e->b_col;
+        c.seg = {e->a_rowptr, nullptr, 0, 0};
+        c.rows = e->n; c.D = e->H; c.r = r; c.out = AH;
+        c.row_len = e->tail_off; c.row_len_stride = stride;
+        c.d_rows = e->n_hot;
+        c.work_counter = e->work_counter; c.err = e->d_err;
+        DN_TRY(spmm_call(c, e->st));
+        accumulate = 1;
+    }
+    for (int b = 0; b < e->n_tail_blocks; b++) {
+        SpmmCall c;
+        c.kind = (e->tail_nnz[(size_t)b] / e->n > 512) ? kSpmmBucketBlock : kSpmmBucketWarp;
+        c.vals = e->b_vals; c.ind = e->b_col;
+        c.seg = {e->a_rowptr, e->tail_off, stride, b};
+        c.rows = e->n; c.D = e->H; c.r = r; c.out = AH;
+        c.accumulate = accumulate;
+        DN_TRY(spmm_call(c, e->st));
+        accumulate = 1;
+    }
+    if (!accumulate) DN_CUDA(cudaMemsetAsync(AH, 0, sizeof(float) * (size_t)(e->n * r), e->st));
+    return DNPEFF_OK;
+}
+
+// A^T*W: the popular columns (long CSC rows) through the tiled kernel with W
+// staged tile by tile, the rest by warp/block gathers from the L2-resident W.
+int spmm_wa(dnpeff_engine* e) {
+    const int r = e->p.rank;
+    if (!spmm_fast_rank(r))
+        return spmm_dispatch(e->c_vals, e->c_row, e->c_colptr, e->ms, e->W, r, e->WA, e->plan_csc, e->st);
+    if (e->n_hot > 0) {
+        SpmmCall c;
+        c.kind = kSpmmTiled;
+        c.vals = e->c_vals; c.ind = e->c_row;
+        c.seg = {e->c_colptr, nullptr, 0, 0};
+        c.rows = e->n_hot; c.D = e->W; c.r = r; c.out = e->WA;
+        c.d_rows = e->n;
+        c.work_counter = e->work_counter; c.err = e->d_err;
+        DN_TRY(spmm_call(c, e->st));
+    }
+    if (e->ms > e->n_hot) {
+        SpmmCall c;
+        c.kind = kSpmmRows;
+        c.vals = e->c_vals; c.ind = e->c_row;
+        c.seg = {e->c_colptr, nullptr, 0, 0};
+        c.row_first = e->n_hot; c.rows = e->ms - e->n_hot;
+        c.D = e->W; c.r = r; c.out = e->WA; c.plan = &e->plan_csc;
+        DN_TRY(spmm_call(c, e->st));
+    }
+    return DNPEFF_OK;
+}
+
 int compute_ah_hh(dnpeff_engine* e) {
     const int r = e->p.rank;
     float* AH = e->AHG;
     float* HH = e->AHG + e->n * r;
     {
         ScopedTimer t(e, 0);
-        DN_TRY(spmm_dispatch(e->a_vals, e->a_col, e->a_rowptr, e->n, e->H, r, AH, e->plan_csr, e->st));
+        DN_TRY(spmm_ah(e, AH));
     }
     {
         ScopedTimer t(e, 2);
@@ -435,7 +616,7 @@ int step_h(dnpeff_engine* e) {
     if (!e->WA) DN_CUDA(cudaMalloc((void**)&e->WA, sizeof(float) * (size_t)std::max<int64_t>(e->ms * r, 1)));
     {
         ScopedTimer t(e, 1);
-        DN_TRY(spmm_dispatch(e->c_vals, e->c_row, e->c_colptr, e->ms, e->W, r, e->WA, e->plan_csc, e->st));
+        DN_TRY(spmm_wa(e));
     }
     {
         ScopedTimer t(e, 2);
@@ -477,6 +658,7 @@ int loss_from_current(dnpeff_engine* e, bool recompute_ah, double* out) {
     double h[2];
     DN_CUDA(cudaMemcpyAsync(h, e->red_out, sizeof(double) * 2, cudaMemcpyDeviceToHost, e->st));
     DN_CUDA(cudaStreamSynchronize(e->st));
+    DN_TRY(check_kernel_status(e));
     double a2 = 0;
     DN_TRY(global_a_sq(e, &a2));
     double sq = a2 + h[1] - 2.0 * h[0];
@@ -493,11 +675,21 @@ int init_generated(dnpeff_engine* e, bool do_w, bool do_h) {
         DN_COUNT_LAUNCH(1);
     }
     if (do_h && e->ms > 0) {
-        k_init_uniform_cols<<<kNumSMs * 8, 256, 0, e->st>>>(e->H, e->ms, r, e->map,
+        k_init_uniform_cols<<<kNumSMs * 8, 256, 0, e->st>>>(e->H, e->ms, r, e->map, e->perm,
                                                           stream_key(e->p.seed, 1), scale);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
     }
+    return DNPEFF_OK;
+}
+
+// Reads the device error word the bounded waits write (synchronises the stream).
+int check_kernel_status(dnpeff_engine* e) {
+    int h = 0;
+    DN_CUDA(cudaMemcpyAsync(&h, e->d_err, sizeof(int), cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    if (h & kErrTiledTimeout)
+        return fail(DNPEFF_ERR_CUDA, "a bulk-copy wait in the tiled SpMM kernel ran out; results are invalid");
     return DNPEFF_OK;
 }
 
@@ -581,7 +773,10 @@ int dnpeff_create(const dnpeff_params* params, int device, void* stream, dnpeff_
         e->own_stream = true;
     }
     if (cudaMalloc((void**)&e->red_partial, sizeof(double) * 2 * kRedBlocks) != cudaSuccess ||
-        cudaMalloc((void**)&e->red_out, sizeof(double) * 4) != cudaSuccess) {
+        cudaMalloc((void**)&e->red_out, sizeof(double) * 4) != cudaSuccess ||
+        cudaMalloc((void**)&e->work_counter, sizeof(int)) != cudaSuccess ||
+        cudaMalloc((void**)&e->d_err, sizeof(int)) != cudaSuccess ||
+        cudaMemset(e->d_err, 0, sizeof(int)) != cudaSuccess) {
         dnpeff_destroy(e);
         return fail(DNPEFF_ERR_CUDA, "cudaMalloc of reduction buffers failed");
     }
@@ -598,6 +793,8 @@ int dnpeff_destroy(dnpeff_engine* e) {
     free_matrix(e);
     dev_free(e->red_partial);
     dev_free(e->red_out);
+    dev_free(e->work_counter);
+    dev_free(e->d_err);
     for (auto& r : e->regions) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
     for (auto ev : e->ev_pool) cudaEventDestroy(ev);
     if (e->own_stream) cudaStreamDestroy(e->st);
@@ -701,10 +898,28 @@ int dnpeff_export_shard_csc(dnpeff_engine* e, int64_t* colptr, int32_t* rowind, 
     DN_TRY(check_ready(e, false));
     DeviceGuard g(e->device);
     DN_TRY(build_csc(e));
-    if (colptr) DN_CUDA(cudaMemcpyAsync(colptr, e->c_colptr, sizeof(int64_t) * (size_t)(e->ms + 1), cudaMemcpyDeviceToHost, e->st));
-    if (rowind && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(rowind, e->c_row, sizeof(int32_t) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
-    if (vals && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(vals, e->c_vals, sizeof(float) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+    // The device CSC is in the engine's internal column order; hand it out in
+    // local column order (a test/debug path: reordered on the host).
+    std::vector<int64_t> cp((size_t)e->ms + 1);
+    std::vector<int32_t> perm((size_t)e->ms), ri((size_t)e->nnz);
+    std::vector<float> va((size_t)e->nnz);
+    DN_CUDA(cudaMemcpyAsync(cp.data(), e->c_colptr, sizeof(int64_t) * (size_t)(e->ms + 1), cudaMemcpyDeviceToHost, e->st));
+    if (e->ms > 0) DN_CUDA(cudaMemcpyAsync(perm.data(), e->inv_perm, sizeof(int32_t) * (size_t)e->ms, cudaMemcpyDeviceToHost, e->st));
+    if (e->nnz > 0) {
+        DN_CUDA(cudaMemcpyAsync(ri.data(), e->c_row, sizeof(int32_t) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+        DN_CUDA(cudaMemcpyAsync(va.data(), e->c_vals, sizeof(float) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+    }
     DN_CUDA(cudaStreamSynchronize(e->st));
+    int64_t q = 0;
+    for (int64_t j = 0; j < e->ms; j++) {
+        int64_t jp = perm[(size_t)j];
+        if (colptr) colptr[j] = q;
+        for (int64_t p = cp[(size_t)jp]; p < cp[(size_t)jp + 1]; p++, q++) {
+            if (rowind) rowind[q] = ri[(size_t)p];
+            if (vals) vals[q] = va[(size_t)p];
+        }
+    }
+    if (colptr) colptr[e->ms] = q;
     return DNPEFF_OK;
 }
 
@@ -736,10 +951,15 @@ int dnpeff_init_factors(dnpeff_engine* e, const float* W, const float* H) {
     if (H && e->ms > 0) {
         DevBuf<float> tmp;
         DN_TRY(tmp.alloc((size_t)(e->ms * r)));
+        DevBuf<float> tmp2;
+        DN_TRY(tmp2.alloc((size_t)(e->ms * r)));
         DN_CUDA(cudaMemcpyAsync(tmp.p, H, sizeof(float) * (size_t)(e->ms * r), cudaMemcpyHostToDevice, e->st));
-        k_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(tmp.p, e->H, r, e->ms);
+        k_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(tmp.p, tmp2.p, r, e->ms);
         DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(1);
+        // internal row jp holds local column perm[jp]
+        k_gather_rows<<<kNumSMs * 8, 256, 0, e->st>>>(tmp2.p, e->perm, e->ms, r, e->H);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(2);
         DN_CUDA(cudaStreamSynchronize(e->st));
     }
     DN_CUDA(cudaStreamSynchronize(e->st));
@@ -752,8 +972,7 @@ int dnpeff_get_w(dnpeff_engine* e, float* out) {
     DeviceGuard g(e->device);
     if (e->n > 0)
         DN_CUDA(cudaMemcpyAsync(out, e->W, sizeof(float) * (size_t)(e->n * e->p.rank), cudaMemcpyDeviceToHost, e->st));
-    DN_CUDA(cudaStreamSynchronize(e->st));
-    return DNPEFF_OK;
+    return check_kernel_status(e);
 }
 
 int dnpeff_get_h(dnpeff_engine* e, float* out) {
@@ -761,17 +980,21 @@ int dnpeff_get_h(dnpeff_engine* e, float* out) {
     DeviceGuard g(e->device);
     const int r = e->p.rank;
     if (e->ms > 0) {
-        DevBuf<float> tmp;
-        float* t = e->WA;
+        DevBuf<float> tmp, tmp2;
+        DN_TRY(tmp.alloc((size_t)(e->ms * r)));
+        float* t = e->WA;  // free between iterations
         if (!t) {
-            DN_TRY(tmp.alloc((size_t)(e->ms * r)));
-            t = tmp.p;
+            DN_TRY(tmp2.alloc((size_t)(e->ms * r)));
+            t = tmp2.p;
         }
-        k_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(e->H, t, e->ms, r);
+        // local column j is internal row inv_perm[j]
+        k_gather_rows<<<kNumSMs * 8, 256, 0, e->st>>>(e->H, e->inv_perm, e->ms, r, tmp.p);
         DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(1);
+        k_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(tmp.p, t, e->ms, r);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(2);
         DN_CUDA(cudaMemcpyAsync(out, t, sizeof(float) * (size_t)(e->ms * r), cudaMemcpyDeviceToHost, e->st));
-        DN_CUDA(cudaStreamSynchronize(e->st));
+        DN_TRY(check_kernel_status(e));
     }
     return DNPEFF_OK;
 }
@@ -818,8 +1041,7 @@ int dnpeff_step_h(dnpeff_engine* e) {
 int dnpeff_synchronize(dnpeff_engine* e) {
     if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
     DeviceGuard g(e->device);
-    DN_CUDA(cudaStreamSynchronize(e->st));
-    return DNPEFF_OK;
+    return check_kernel_status(e);
 }
 
 int dnpeff_loss(dnpeff_engine* e, double* out) {
@@ -915,7 +1137,7 @@ int dnpeff_op_spmm(const float* vals, const int32_t* ind, const int64_t* ptr, in
     cudaStream_t st = (cudaStream_t)stream;
     SpmmPlan plan;
     plan.n_short = rows;
-    if (spmm_fast_rank(r)) DN_TRY(spmm_make_plan(ptr, rows, &plan, st));
+    if (spmm_fast_rank(r)) DN_TRY(spmm_make_plan(ptr, 0, rows, &plan, st));
     int s = spmm_dispatch(vals, ind, ptr, rows, D, r, out, plan, st);
     if (plan.long_list) {
         cudaStreamSynchronize(st);

@@ -265,6 +265,142 @@ __global__ void k_csc_advance(const int64_t* __restrict__ rowptr,
     }
 }
 
+// ---- internal column order and row buckets -----------------------------------
+// The engine renumbers a shard's columns as [popular ("hot") columns in id
+// order][the rest in id order].  hot_pos is the exclusive scan of the hot flags.
+__global__ void k_hot_flags(const int32_t* __restrict__ col_count, int64_t n_cols, int32_t threshold,
+                            int32_t* __restrict__ flags) {
+    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n_cols) flags[j] = col_count[j] >= threshold ? 1 : 0;
+    else if (j == n_cols) flags[j] = 0;
+}
+
+__global__ void k_build_perm(const int32_t* __restrict__ flags, const int64_t* __restrict__ hot_pos,
+                             int64_t n_cols, int64_t n_hot, int32_t* __restrict__ perm,
+                             int32_t* __restrict__ inv_perm) {
+    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n_cols) return;
+    int64_t jp = flags[j] ? hot_pos[j] : n_hot + (j - hot_pos[j]);
+    inv_perm[j] = (int32_t)jp;
+    perm[jp] = (int32_t)j;
+}
+
+// cnt_p[jp] = col_count[perm[jp]] (+ a trailing zero for the scan).
+__global__ void k_permute_counts(const int32_t* __restrict__ col_count, const int32_t* __restrict__ perm,
+                                 int64_t n_cols, int32_t* __restrict__ cnt_p) {
+    int64_t jp = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (jp < n_cols) cnt_p[jp] = col_count[perm[jp]];
+    else if (jp == n_cols) cnt_p[jp] = 0;
+}
+
+// Bucket of an internal column: hot columns are cut into tiles of `tile` columns
+// (buckets 0..n_hot_tiles-1), the rest into blocks of `block` columns.
+struct BucketMap {
+    int64_t n_hot;
+    int32_t tile, block, n_hot_tiles, n_buckets;
+    __host__ __device__ int bucket(int64_t jp) const {
+        return jp < n_hot ? (int)(jp / tile) : n_hot_tiles + (int)((jp - n_hot) / block);
+    }
+};
+
+// Stable partition of every row's entries by bucket (one block of 8 warps per
+// row, dynamic shared memory 8 * n_buckets ints).  Input: the shard's CSR with
+// local column ids; output: the same rows with internal column ids, entries
+// grouped by ascending bucket, original order kept inside a bucket, plus
+// tail_off[row][b] = offset inside the row of tail block b (b = 0 is the end of
+// the hot part; n_tail_blocks + 1 entries per row).
+__global__ void __launch_bounds__(256)
+k_bucket_rows(const float* __restrict__ vals, const int32_t* __restrict__ col,
+              const int64_t* __restrict__ rowptr, int64_t n_rows, const int32_t* __restrict__ inv_perm,
+              BucketMap bm, float* __restrict__ out_vals, int32_t* __restrict__ out_col,
+              uint32_t* __restrict__ tail_off) {
+    extern __shared__ int cnt[];  // [8][n_buckets]
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int NB = bm.n_buckets;
+    const int n_tail = NB - bm.n_hot_tiles;
+    for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+        const int64_t beg = rowptr[row], end = rowptr[row + 1];
+        const int64_t len = end - beg;
+        int64_t chunk = ((len + 7) / 8 + 31) / 32 * 32;  // per-warp share, a multiple of 32
+        const int64_t wb = beg + w * chunk < end ? beg + w * chunk : end;
+        const int64_t we = wb + chunk < end ? wb + chunk : end;
+        for (int i = threadIdx.x; i < 8 * NB; i += 256) cnt[i] = 0;
+        __syncthreads();
+        // 1. per-warp bucket counts
+        for (int64_t base = wb; base < we; base += 32) {
+            int64_t p = base + lane;
+            int b = -1 - lane;  // inactive lanes: distinct negative keys
+            if (p < we) b = bm.bucket(inv_perm[col[p]]);
+            unsigned peers = __match_any_sync(0xffffffffu, b);
+            if (p < we && lane == __ffs(peers) - 1) cnt[w * NB + b] += __popc(peers);
+            __syncwarp();
+        }
+        __syncthreads();
+        // 2. start of every (bucket, warp) run: buckets ascending, warps ascending inside
+        if (w == 0) {
+            int run = 0;
+            for (int b0 = 0; b0 < NB; b0 += 32) {
+                int b = b0 + lane;
+                int tot = 0;
+                if (b < NB)
+                    for (int ww = 0; ww < 8; ww++) tot += cnt[ww * NB + b];
+                int inc = tot;
+                for (int o = 1; o < 32; o <<= 1) {
+                    int t = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += t;
+                }
+                int start = run + inc - tot;
+                if (b < NB) {
+                    if (b >= bm.n_hot_tiles) tail_off[row * (n_tail + 1) + (b - bm.n_hot_tiles)] = (uint32_t)start;
+                    for (int ww = 0; ww < 8; ww++) {
+                        int c = cnt[ww * NB + b];
+                        cnt[ww * NB + b] = start;
+                        start += c;
+                    }
+                }
+                run += __shfl_sync(0xffffffffu, inc, 31);
+            }
+            if (lane == 0) tail_off[row * (n_tail + 1) + n_tail] = (uint32_t)len;
+        }
+        __syncthreads();
+        // 3. stable scatter
+        for (int64_t base = wb; base < we; base += 32) {
+            int64_t p = base + lane;
+            int b = -1 - lane;
+            int jp = 0;
+            float v = 0.f;
+            if (p < we) {
+                jp = inv_perm[col[p]];
+                b = bm.bucket(jp);
+                v = vals[p];
+            }
+            unsigned peers = __match_any_sync(0xffffffffu, b);
+            if (p < we) {
+                int rank = __popc(peers & ((1u << lane) - 1u));
+                int64_t q = beg + cnt[w * NB + b] + rank;
+                out_col[q] = jp;
+                out_vals[q] = v;
+            }
+            __syncwarp();
+            if (p < we && lane == __ffs(peers) - 1) cnt[w * NB + b] += __popc(peers);
+            __syncwarp();
+        }
+        __syncthreads();
+    }
+}
+
+// rows_out[i] = rows_in[index[i]] for r floats per row (float4 when r % 4 == 0).
+__global__ void k_gather_rows(const float* __restrict__ in, const int32_t* __restrict__ index,
+                              int64_t n_rows, int r, float* __restrict__ out) {
+    int64_t total = n_rows * r;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        int64_t row = i / r;
+        int c = (int)(i - row * r);
+        out[i] = in[(int64_t)index[row] * r + c];
+    }
+}
+
 // ---- reductions over the stored values --------------------------------------
 // partial[b] = (sum v, sum v*v) of block b, then one block folds the partials in
 // index order: double accumulation, fixed order.
@@ -319,14 +455,16 @@ __global__ void k_init_uniform(float* __restrict__ out, int64_t first, int64_t c
 
 // H[j, t] = scale * U(0,1] at global index (global column of j) * r + t, so every
 // sharding of the feature axis starts from the same matrix.
+// Row jp of `out` is internal column jp = local column perm[jp].
 __global__ void k_init_uniform_cols(float* __restrict__ out, int64_t n_local_cols, int r,
-                                    ShardMap map, uint64_t key, float scale) {
+                                    ShardMap map, const int32_t* __restrict__ perm, uint64_t key,
+                                    float scale) {
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     int64_t count = n_local_cols * r;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
-        int64_t j = i / r;
-        int t = (int)(i - j * r);
-        out[i] = uniform01_from_key(key, (uint64_t)(map.global(j) * r + t)) * scale;
+        int64_t jp = i / r;
+        int t = (int)(i - jp * r);
+        out[i] = uniform01_from_key(key, (uint64_t)(map.global(perm[jp]) * r + t)) * scale;
     }
 }
 
