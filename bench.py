@@ -283,6 +283,7 @@ def main():
     eng.set_init_scale(global_scale(eng))
     eng.init_factors()
     _, m_kept, c0, ms, nnz = eng.shape
+    layout = eng.layout()
 
     def barrier():
         if world > 1:
@@ -395,7 +396,8 @@ def main():
             "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name(cfg_id, c), "n_cols_kept": m_kept,
-                       "nnz_per_rank": nnz, "shard": "columns/%d%s" % (world, " cyclic" if world > 1 else ""),
+                       "nnz_per_rank": nnz, "popular_cols": layout[0], "popular_nnz": layout[1],
+                       "tail_blocks": layout[2], "shard": "columns/%d%s" % (world, " cyclic" if world > 1 else ""),
                        "l2": "inputs larger than L2 (A %.1f GB, H %.2f GB per rank)" % (
                            16.0 * nnz / 1e9, 4.0 * r * ms / 1e9),
                        "setup_s": {"generate": round(t_gen, 2), "load_resident": round(t_load, 2)},

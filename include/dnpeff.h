@@ -107,6 +107,12 @@ int dnpeff_set_csr_device(dnpeff_engine* eng, int64_t n_rows, int64_t n_cols_ful
  * (getSizeOfSplit, src/util/matrix_util.h:10-20). */
 int dnpeff_get_shape(dnpeff_engine* eng, int64_t* n_rows, int64_t* n_cols_kept,
                      int64_t* col_start, int64_t* n_cols_shard, int64_t* nnz_shard);
+/* How the engine laid the shard out internally (no reference counterpart;
+ * reported by the benchmark): columns held by at least 1/8 of the rows are
+ * "popular" and go through the shared-memory tiled SpMM kernel, the rest is cut
+ * into column blocks whose slice of H stays L2-resident while it is gathered. */
+int dnpeff_get_layout(dnpeff_engine* eng, int64_t* n_popular_cols, int64_t* popular_nnz,
+                      int32_t* n_tail_blocks, int32_t* tile_rows);
 /* newToOgIndex of removeSmallestL0NormColumns_inPlace: n_cols_kept original ids. */
 int dnpeff_get_new_to_og(dnpeff_engine* eng, int32_t* out);
 /* For each of the n_cols_shard local columns: its index among the kept columns

@@ -39,6 +39,7 @@ SIGNATURES = {
     "dnpeff_set_csr": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_set_csr_device": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_get_shape": (C.c_int, [_P] + [C.POINTER(_I64)] * 5),
+    "dnpeff_get_layout": (C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I32), C.POINTER(_I32)]),
     "dnpeff_get_new_to_og": (C.c_int, [_P, _P]),
     "dnpeff_get_shard_columns": (C.c_int, [_P, _P, _P]),
     "dnpeff_export_shard_csr": (C.c_int, [_P, _P, _P, _P]),

@@ -858,6 +858,20 @@ int dnpeff_get_shape(dnpeff_engine* e, int64_t* n_rows, int64_t* n_cols_kept, in
     return DNPEFF_OK;
 }
 
+int dnpeff_get_layout(dnpeff_engine* e, int64_t* n_hot_cols, int64_t* hot_nnz, int32_t* n_tail_blocks,
+                      int32_t* tile_rows) {
+    DN_TRY(check_ready(e, false));
+    DeviceGuard g(e->device);
+    int64_t v = 0;
+    DN_CUDA(cudaMemcpyAsync(&v, e->c_colptr + e->n_hot, sizeof(int64_t), cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    if (n_hot_cols) *n_hot_cols = e->n_hot;
+    if (hot_nnz) *hot_nnz = v;
+    if (n_tail_blocks) *n_tail_blocks = e->n_tail_blocks;
+    if (tile_rows) *tile_rows = e->bm.tile;
+    return DNPEFF_OK;
+}
+
 int dnpeff_get_new_to_og(dnpeff_engine* e, int32_t* out) {
     DN_TRY(check_ready(e, false));
     DeviceGuard g(e->device);

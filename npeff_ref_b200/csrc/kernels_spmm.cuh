@@ -32,6 +32,11 @@ __device__ __forceinline__ void spmm_accumulate(const float* __restrict__ vals,
     constexpr int U = (V >= 8) ? 1 : (8 / V);
     const int lane = threadIdx.x & 31;
     const int g = lane / G, l = lane % G;
+    // Lanes past the end of the row (r4 not a multiple of G) gather the last
+    // float4 instead: their accumulators are never stored, so no masking is needed.
+    int cq[V];
+#pragma unroll
+    for (int q = 0; q < V; q++) cq[q] = (l + G * q < r4) ? l + G * q : r4 - 1;
     for (int64_t base = beg; base < end; base += chunk_stride) {
         int64_t p = base + lane;
         float v = 0.f;
@@ -57,10 +62,7 @@ __device__ __forceinline__ void spmm_accumulate(const float* __restrict__ vals,
             for (int u = 0; u < U; u++) {
                 const float4* drow = D4 + (int64_t)jj[u] * r4;
 #pragma unroll
-                for (int q = 0; q < V; q++) {
-                    int c = l + G * q;
-                    h[u][q] = (c < r4) ? __ldg(drow + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+                for (int q = 0; q < V; q++) h[u][q] = __ldg(drow + cq[q]);
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
@@ -201,10 +203,15 @@ k_spmm_block(const float* __restrict__ vals, const int32_t* __restrict__ ind, Se
 // walks its entries tile by tile: the entries of a row must be grouped by tile
 // in ascending tile order (any order inside a tile).
 //
-// Persistent blocks fetch groups of kTiledWarps rows from an atomic counter.
+// Persistent blocks fetch groups of rows (one per warp) from an atomic counter.
 // Every wait on the copy barrier is bounded: on expiry the block records the
 // error and leaves without touching the output again.
-constexpr int kTiledWarps = 16;
+// Warps (= rows) per block of the tiled kernel: 32 while the kernel fits 64
+// registers per thread (up to 4 float4 accumulators per lane), 16 above.
+template <int V>
+struct TiledWarps {
+    static constexpr int value = (V <= 4) ? 32 : 16;
+};
 constexpr uint32_t kTiledSpinLimit = 1u << 24;
 enum : int { kErrTiledTimeout = 8 };
 
@@ -243,7 +250,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 }
 
 template <int G, int V>
-__global__ void __launch_bounds__(kTiledWarps * 32, 1)
+__global__ void __launch_bounds__(TiledWarps<V>::value * 32, 1)
 k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
              const int64_t* __restrict__ ptr, const uint32_t* __restrict__ row_len,
              int row_len_stride, int64_t rows, const float* __restrict__ D, int r4, int64_t d_rows, int tile_rows,
@@ -254,10 +261,14 @@ k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
     __shared__ int s_group;
     constexpr int NG = 32 / G;
     constexpr int U = (V >= 8) ? 1 : (8 / V);
+    constexpr int kTiledWarps = TiledWarps<V>::value;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int g = lane / G, l = lane % G;
     const size_t tile_floats4 = (size_t)tile_rows * r4;
     float4* const tile0 = (float4*)smem_raw;
+    const uint32_t tile_smem = smem_u32(smem_raw);
+    const uint32_t row_bytes = (uint32_t)r4 * 16u;
+    const uint32_t tile_bytes = (uint32_t)tile_rows * row_bytes;
     const int n_tiles = (int)((d_rows + tile_rows - 1) / tile_rows);
     const int64_t n_groups = (rows + kTiledWarps - 1) / kTiledWarps;
 
@@ -268,6 +279,11 @@ k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
     }
     __syncthreads();
     uint32_t phase_bits = 0;  // bit b: parity the next wait on buffer b expects
+    // byte offset of this lane's float4s inside a tile row; lanes past the end of
+    // the row read the last float4 (their accumulators are never stored)
+    uint32_t lane_off[V];
+#pragma unroll
+    for (int q = 0; q < V; q++) lane_off[q] = (uint32_t)((l + G * q < r4) ? l + G * q : r4 - 1) * 16u;
 
     auto issue = [&](int t) {  // thread 0 only
         int64_t first = (int64_t)t * tile_rows;
@@ -292,20 +308,45 @@ k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
         for (int q = 0; q < V; q++) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
 
         if (threadIdx.x == 0) issue(0);
-        // the 32 stored entries at the cursor, reloaded as soon as the cursor moves so
-        // that the load is in flight while the block waits for the next tile
-        float v = 0.f;
-        int j = INT32_MAX;
-        auto load_chunk = [&]() {
+        // A window of 64 stored entries is kept in registers: (v, j) are the 32 at the
+        // cursor, (vb, jb) the 32 after them.  When the cursor moves the window is
+        // re-aligned with shuffles and only the far half is fetched again, so the
+        // entries needed next are always already on their way.
+        float v = 0.f, vb = 0.f;
+        int j = INT32_MAX, jb = INT32_MAX;
+        auto load_far = [&]() {
+            int64_t p = cursor + 32 + lane;
+            vb = 0.f;
+            jb = INT32_MAX;
+            if (p < end) {
+                vb = __ldcs(vals + p);
+                jb = __ldcs(ind + p);
+            }
+        };
+        {
             int64_t p = cursor + lane;
-            v = 0.f;
-            j = INT32_MAX;
             if (p < end) {
                 v = __ldcs(vals + p);
                 j = __ldcs(ind + p);
             }
+            load_far();
+        }
+        auto advance = [&](int cnt) {
+            cursor += cnt;
+            if (cnt == 32) {
+                v = vb;
+                j = jb;
+            } else {
+                const int src = lane + cnt;
+                const float v0 = __shfl_sync(0xffffffffu, v, src & 31);
+                const float v1 = __shfl_sync(0xffffffffu, vb, src & 31);
+                const int j0 = __shfl_sync(0xffffffffu, j, src & 31);
+                const int j1 = __shfl_sync(0xffffffffu, jb, src & 31);
+                v = src < 32 ? v0 : v1;
+                j = src < 32 ? j0 : j1;
+            }
+            load_far();
         };
-        load_chunk();
         bool ok = true;
         for (int t = 0; t < n_tiles; t++) {
             const int buf = t & 1;
@@ -313,7 +354,8 @@ k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
             if (!mbar_wait(&full_bar[buf], (phase_bits >> buf) & 1u)) ok = false;
             phase_bits ^= 1u << buf;
             if (!__syncthreads_and(ok ? 1 : 0)) { ok = false; break; }
-            const float4* tl = tile0 + (size_t)buf * tile_floats4;
+            // 32-bit shared-memory address of this lane's 16 bytes of tile row 0
+            const uint32_t buf_base = tile_smem + (uint32_t)buf * tile_bytes;
             const int64_t tile_base = (int64_t)t * tile_rows;
             const int64_t tile_end = tile_base + tile_rows;
             while (true) {
@@ -321,25 +363,26 @@ k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
                 const unsigned mask = __ballot_sync(0xffffffffu, in);
                 const int cnt = __popc(mask);  // entries are grouped by tile: a prefix of the chunk
                 if (cnt == 0) break;
-                const int jl = in ? (int)((int64_t)j - tile_base) : 0;
+                // byte offset of the gathered tile row, computed once by the owning lane
+                const uint32_t off = in ? (uint32_t)((int64_t)j - tile_base) * row_bytes : 0u;
                 const float vz = in ? v : 0.f;
                 for (int t0 = 0; t0 < cnt; t0 += NG * U) {
                     float vv[U];
-                    int jj[U];
+                    uint32_t oo[U];
 #pragma unroll
                     for (int u = 0; u < U; u++) {
                         int src = t0 + u * NG + g;
                         vv[u] = __shfl_sync(0xffffffffu, vz, src);
-                        jj[u] = __shfl_sync(0xffffffffu, jl, src);
+                        oo[u] = __shfl_sync(0xffffffffu, off, src);
                     }
                     float4 h[U][V];
 #pragma unroll
                     for (int u = 0; u < U; u++) {
-                        const float4* drow = tl + (size_t)jj[u] * r4;
 #pragma unroll
                         for (int q = 0; q < V; q++) {
-                            int c = l + G * q;
-                            h[u][q] = (c < r4) ? drow[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(h[u][q].x), "=f"(h[u][q].y), "=f"(h[u][q].z), "=f"(h[u][q].w)
+                                         : "r"(buf_base + oo[u] + lane_off[q]));
                         }
                     }
 #pragma unroll
@@ -353,8 +396,7 @@ k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
                         }
                     }
                 }
-                cursor += cnt;
-                load_chunk();
+                advance(cnt);
                 if (cnt < 32) break;
             }
             __syncthreads();  // everybody is done with this buffer before it is refilled
@@ -486,6 +528,7 @@ inline int spmm_launch_t(const SpmmCall& c, cudaStream_t st) {
             DN_CUDA(cudaFuncSetAttribute(k_spmm_tiled<G, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
             DN_CUDA(cudaMemsetAsync(c.work_counter, 0, sizeof(int), st));
+            constexpr int kTiledWarps = TiledWarps<V>::value;
             int64_t groups = ceil_div(c.rows, kTiledWarps);
             int grid = (int)(groups < kNumSMs ? groups : kNumSMs);
             k_spmm_tiled<G, V><<<grid, kTiledWarps * 32, smem, st>>>(
@@ -504,6 +547,20 @@ inline int spmm_call(const SpmmCall& c, cudaStream_t st) {
     if (!spmm_fast_rank(c.r)) return fail(DNPEFF_ERR_INVALID, "internal: fast SpMM called with rank %d", c.r);
 #define DN_SPMM_CASE(G, V) return spmm_launch_t<G, V>(c, st)
     int r4 = c.r / 4;
+    if (c.kind == kSpmmTiled) {
+        // Shared-memory gathers: groups of 8 lanes (128 bytes of the tile row per
+        // group and load) keep four entries in flight per warp instruction and need
+        // a quarter of the shuffles of a whole-warp-per-entry layout; shuffles and
+        // shared loads share the pipe that bounds this kernel.
+        if (r4 <= 8) DN_SPMM_CASE(8, 1);
+        if (r4 <= 16) DN_SPMM_CASE(8, 2);
+        if (r4 <= 32) DN_SPMM_CASE(8, 4);
+        if (r4 <= 64) DN_SPMM_CASE(8, 8);
+        if (r4 <= 128) DN_SPMM_CASE(16, 8);
+        DN_SPMM_CASE(32, 8);
+    }
+    // L2/HBM gathers: one whole row of D per warp-wide 128-bit load where r allows
+    // (measured faster than the grouped layout for these).
     if (r4 <= 8) DN_SPMM_CASE(8, 1);
     if (r4 <= 16) DN_SPMM_CASE(16, 1);
     if (r4 <= 32) DN_SPMM_CASE(32, 1);

@@ -95,6 +95,12 @@ class MuNmf:
         check(lib().dnpeff_get_shape(self._h, *[C.byref(x) for x in v]))
         return tuple(x.value for x in v)
 
+    def layout(self):
+        """(n_popular_cols, popular_nnz, n_tail_blocks, tile_rows) of the internal layout."""
+        a, b, c, d = C.c_int64(0), C.c_int64(0), C.c_int32(0), C.c_int32(0)
+        check(lib().dnpeff_get_layout(self._h, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+        return a.value, b.value, c.value, d.value
+
     def new_to_og(self):
         out = np.empty(max(self.shape[1], 1), dtype=np.int32)
         check(lib().dnpeff_get_new_to_og(self._h, _ptr(out)))
