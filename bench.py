@@ -357,15 +357,20 @@ def main():
         join(eng2)
         barrier()
         ev0.record()
+        tw = [time.perf_counter()]
         check(lib().dnpeff_set_csr(eng2._h, n, m, k, None, h_vals.data_ptr(), h_idx.data_ptr(),
                                    h_norms.data_ptr(), 1))
+        tw.append(time.perf_counter())
         eng2.set_init_scale(global_scale(eng2))
         eng2.init_factors()
         for _ in range(args.steps):
             eng2.step_w()
             eng2.step_h()
+        eng2.synchronize()
+        tw.append(time.perf_counter())
         check(lib().dnpeff_get_w(eng2._h, W_out.data_ptr()))
         check(lib().dnpeff_get_h(eng2._h, H_out.data_ptr()))
+        tw.append(time.perf_counter())
         ev1.record()
         barrier()
         te = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device="cuda")
@@ -377,6 +382,8 @@ def main():
         e2e = {"value": args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps,
                "ms_total": e2e_ms,
+               "host_ms": {"load": round(1e3 * (tw[1] - tw[0]), 1), "iterate": round(1e3 * (tw[2] - tw[1]), 1),
+                           "read_back": round(1e3 * (tw[3] - tw[2]), 1)},
                "what": "dnpeff_set_csr from pinned host arrays (upload, normalise, prune, shard, CSC) "
                        "+ init + K iterations + dnpeff_get_w/get_h into pinned host arrays"}
         eng2.close()

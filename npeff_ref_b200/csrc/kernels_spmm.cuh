@@ -261,7 +261,7 @@ k_spmm_tiled(const float* __restrict__ vals, const int32_t* __restrict__ ind,
     __shared__ int s_group;
     constexpr int NG = 32 / G;
     constexpr int U = (V >= 8) ? 1 : (8 / V);
-    constexpr int kTiledWarps = TiledWarps<V>::value;
+    const int kTiledWarps = blockDim.x >> 5;  // rows per group, chosen by the launcher
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int g = lane / G, l = lane % G;
     const size_t tile_floats4 = (size_t)tile_rows * r4;
@@ -528,10 +528,17 @@ inline int spmm_launch_t(const SpmmCall& c, cudaStream_t st) {
             DN_CUDA(cudaFuncSetAttribute(k_spmm_tiled<G, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
             DN_CUDA(cudaMemsetAsync(c.work_counter, 0, sizeof(int), st));
-            constexpr int kTiledWarps = TiledWarps<V>::value;
-            int64_t groups = ceil_div(c.rows, kTiledWarps);
+            // Rows per group (= warps per block): the smallest count that lets every
+            // SM take the same whole number of groups, so the last round is full.
+            constexpr int kMaxWarps = TiledWarps<V>::value;
+            int warps = kMaxWarps;
+            for (int k = 1; k <= 64; k++) {
+                int64_t per = ceil_div(c.rows, (int64_t)kNumSMs * k);
+                if (per <= kMaxWarps) { warps = (int)(per < 4 ? 4 : per); break; }
+            }
+            int64_t groups = ceil_div(c.rows, warps);
             int grid = (int)(groups < kNumSMs ? groups : kNumSMs);
-            k_spmm_tiled<G, V><<<grid, kTiledWarps * 32, smem, st>>>(
+            k_spmm_tiled<G, V><<<grid, warps * 32, smem, st>>>(
                 c.vals, c.ind, c.seg.ptr, c.row_len, c.row_len_stride, c.rows, c.D, r4, c.d_rows, tile_rows, out4,
                 c.accumulate, c.work_counter, c.err);
             DN_LAUNCH_CHECK();
