@@ -17,6 +17,7 @@
 #include "kernels_dense.cuh"
 #include "kernels_prep.cuh"
 #include "kernels_spmm.cuh"
+#include "kernels_tc.cuh"
 #include "nccl_dyn.h"
 
 using namespace dnpeff;
@@ -132,6 +133,7 @@ struct dnpeff_engine {
     float* WW = nullptr;   // [r*r]
     float* gram_scratch = nullptr;
     size_t gram_scratch_floats = 0;
+    float* tc_scratch = nullptr;  // 2*r*r: the update's small matrix split for the tensor cores
     double* red_partial = nullptr;  // device, 2*kRedBlocks doubles
     double* red_out = nullptr;      // device, 4 doubles
     SpmmPlan plan_csr, plan_csc;
@@ -198,6 +200,36 @@ struct ScopedTimer {
     }
 };
 
+// DNPEFF_NO_TC=1 keeps the dense contractions on the CUDA-core kernels (A/B runs).
+bool tensor_cores_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* s = getenv("DNPEFF_NO_TC");
+        v = (s && s[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// G = X^T X: tcgen05 kernel where the rank allows, CUDA-core kernel otherwise.
+int gram_any(const float* X, int64_t rows, int r, float* G, float* scratch, int* err, cudaStream_t st) {
+    if (tensor_cores_enabled() && gram_tc_ok(r)) return gram_tc_launch(X, rows, r, G, scratch, err, st);
+    return gram_launch(X, rows, r, G, scratch, st);
+}
+
+size_t gram_any_scratch(int64_t rows, int r) {
+    size_t a = gram_plan(rows, r).scratch_floats;
+    size_t b = gram_tc_ok(r) ? gram_tc_plan(rows, r).scratch_floats : 0;
+    return a > b ? a : b;
+}
+
+// tc_scratch: 2*r*r floats.
+int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int r, float eps,
+                  float* tc_scratch, int* err, cudaStream_t st) {
+    if (tensor_cores_enabled() && mu_update_tc_ok(r))
+        return mu_update_tc_launch(X, Num, G, rows, r, eps, tc_scratch, err, st);
+    return mu_update_launch(X, Num, G, rows, r, eps, st);
+}
+
 void free_matrix(dnpeff_engine* e) {
     dev_free(e->a_vals); dev_free(e->a_col); dev_free(e->a_rowptr);
     dev_free(e->c_vals); dev_free(e->c_row); dev_free(e->c_colptr);
@@ -208,6 +240,7 @@ void free_matrix(dnpeff_engine* e) {
     e->n_hot = 0; e->n_tail_blocks = 0;
     dev_free(e->W); dev_free(e->H); dev_free(e->AHG); dev_free(e->WA); dev_free(e->WW);
     dev_free(e->gram_scratch);
+    dev_free(e->tc_scratch);
     e->gram_scratch_floats = 0;
     dev_free(e->plan_csr.long_list);
     dev_free(e->plan_csc.long_list);
@@ -460,8 +493,9 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_CUDA(cudaMalloc((void**)&e->H, sizeof(float) * (size_t)std::max<int64_t>(ms * r, 1)));
     DN_CUDA(cudaMalloc((void**)&e->AHG, sizeof(float) * (size_t)(n * r + (int64_t)r * r)));
     DN_CUDA(cudaMalloc((void**)&e->WW, sizeof(float) * (size_t)((int64_t)r * r)));
-    e->gram_scratch_floats = std::max(gram_plan(n, r).scratch_floats, gram_plan(ms, r).scratch_floats);
+    e->gram_scratch_floats = std::max(gram_any_scratch(n, r), gram_any_scratch(ms, r));
     DN_CUDA(cudaMalloc((void**)&e->gram_scratch, sizeof(float) * e->gram_scratch_floats));
+    DN_CUDA(cudaMalloc((void**)&e->tc_scratch, sizeof(float) * 2 * (size_t)r * r));
     DN_TRY(spmm_make_plan(e->a_rowptr, 0, n, &e->plan_csr, st));
     DN_TRY(spmm_make_plan(e->c_colptr, e->n_hot, ms - e->n_hot, &e->plan_csc, st));
     e->loaded = true;
@@ -597,7 +631,7 @@ int compute_ah_hh(dnpeff_engine* e) {
     }
     {
         ScopedTimer t(e, 2);
-        DN_TRY(gram_launch(e->H, e->ms, r, HH, e->gram_scratch, e->st));
+        DN_TRY(gram_any(e->H, e->ms, r, HH, e->gram_scratch, e->d_err, e->st));
     }
     DN_TRY(allreduce_f32(e, e->AHG, (size_t)(e->n * r + (int64_t)r * r)));
     return DNPEFF_OK;
@@ -607,7 +641,7 @@ int step_w(dnpeff_engine* e) {
     const int r = e->p.rank;
     DN_TRY(compute_ah_hh(e));
     ScopedTimer t(e, 3);
-    return mu_update_launch(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->st);
+    return mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st);
 }
 
 int step_h(dnpeff_engine* e) {
@@ -620,10 +654,10 @@ int step_h(dnpeff_engine* e) {
     }
     {
         ScopedTimer t(e, 2);
-        DN_TRY(gram_launch(e->W, e->n, r, e->WW, e->gram_scratch, e->st));
+        DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st));
     }
     ScopedTimer t(e, 3);
-    return mu_update_launch(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->st);
+    return mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st);
 }
 
 int global_a_sq(dnpeff_engine* e, double* out) {
@@ -652,7 +686,7 @@ int loss_from_current(dnpeff_engine* e, bool recompute_ah, double* out) {
     const int r = e->p.rank;
     ScopedTimer t(e, 5);
     if (recompute_ah) DN_TRY(compute_ah_hh(e));
-    DN_TRY(gram_launch(e->W, e->n, r, e->WW, e->gram_scratch, e->st));
+    DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st));
     DN_TRY(device_dot(e, e->AHG, e->W, e->n * r, e->red_out + 0));
     DN_TRY(device_dot(e, e->WW, e->AHG + e->n * r, (int64_t)r * r, e->red_out + 1));
     double h[2];
@@ -690,6 +724,8 @@ int check_kernel_status(dnpeff_engine* e) {
     DN_CUDA(cudaStreamSynchronize(e->st));
     if (h & kErrTiledTimeout)
         return fail(DNPEFF_ERR_CUDA, "a bulk-copy wait in the tiled SpMM kernel ran out; results are invalid");
+    if (h & kErrTcTimeout)
+        return fail(DNPEFF_ERR_CUDA, "a wait in a tensor-core kernel ran out; results are invalid");
     return DNPEFF_OK;
 }
 
@@ -706,6 +742,7 @@ struct OpWorkspace {
     std::mutex mu;
     float* scratch[64] = {nullptr};
     size_t floats[64] = {0};
+    int* err[64] = {nullptr};
 };
 OpWorkspace& op_ws() {
     static OpWorkspace w;
@@ -729,6 +766,32 @@ int op_scratch(size_t floats, float** out) {
         w.floats[dev] = floats;
     }
     *out = w.scratch[dev];
+    return DNPEFF_OK;
+}
+
+// Error word of the single-kernel entry points (one per device), read after the call.
+int op_err_word(int** out) {
+    int dev = 0;
+    DN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(DNPEFF_ERR_UNSUPPORTED, "device ordinal %d", dev);
+    OpWorkspace& w = op_ws();
+    std::lock_guard<std::mutex> lk(w.mu);
+    if (!w.err[dev]) {
+        DN_CUDA(cudaMalloc((void**)&w.err[dev], sizeof(int)));
+        DN_CUDA(cudaMemset(w.err[dev], 0, sizeof(int)));
+    }
+    *out = w.err[dev];
+    return DNPEFF_OK;
+}
+
+int op_check_err(int* d_err, cudaStream_t st) {
+    int h = 0;
+    DN_CUDA(cudaMemcpyAsync(&h, d_err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    DN_CUDA(cudaStreamSynchronize(st));
+    if (h) {
+        cudaMemsetAsync(d_err, 0, sizeof(int), st);
+        return fail(DNPEFF_ERR_CUDA, "a bounded wait inside a kernel ran out (status %d); results are invalid", h);
+    }
     return DNPEFF_OK;
 }
 
@@ -1103,7 +1166,7 @@ int dnpeff_fit_w_only(dnpeff_engine* e, int32_t iters, double* loss) {
     DN_TRY(compute_ah_hh(e));
     for (int it = 0; it < iters; it++) {
         ScopedTimer t(e, 3);
-        DN_TRY(mu_update_launch(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->st));
+        DN_TRY(mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st));
     }
     if (loss) DN_TRY(loss_from_current(e, false, loss));
     return DNPEFF_OK;
@@ -1163,14 +1226,22 @@ int dnpeff_op_spmm(const float* vals, const int32_t* ind, const int64_t* ptr, in
 int dnpeff_op_gram(const float* X, int64_t rows, int32_t r, float* G, void* stream) {
     if (rows < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
     float* scratch = nullptr;
-    DN_TRY(op_scratch(gram_plan(rows, r).scratch_floats, &scratch));
-    return gram_launch(X, rows, r, G, scratch, (cudaStream_t)stream);
+    int* err = nullptr;
+    DN_TRY(op_scratch(gram_any_scratch(rows, r), &scratch));
+    DN_TRY(op_err_word(&err));
+    DN_TRY(gram_any(X, rows, r, G, scratch, err, (cudaStream_t)stream));
+    return op_check_err(err, (cudaStream_t)stream);
 }
 
 int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows, int32_t r,
                         float eps, void* stream) {
     if (rows < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
-    return mu_update_launch(X, Num, G, rows, r, eps, (cudaStream_t)stream);
+    float* scratch = nullptr;
+    int* err = nullptr;
+    DN_TRY(op_scratch(2 * (size_t)r * r, &scratch));
+    DN_TRY(op_err_word(&err));
+    DN_TRY(mu_update_any(X, Num, G, rows, r, eps, scratch, err, (cudaStream_t)stream));
+    return op_check_err(err, (cudaStream_t)stream);
 }
 
 }  // extern "C"

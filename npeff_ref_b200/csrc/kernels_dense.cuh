@@ -120,7 +120,9 @@ static __global__ void k_gram_reduce(const float* __restrict__ partial, int nsla
     if (idx >= r * r) return;
     int a = idx / r, b = idx % r;
     int ti = a / tile, tj = b / tile, ea = a % tile, eb = b % tile;
-    if (ti > tj) {
+    // read the upper triangle only (also inside a diagonal tile), so that the
+    // result is symmetric bit for bit whatever computed the tiles
+    if (ti > tj || (ti == tj && ea > eb)) {
         int t = ti; ti = tj; tj = t;
         t = ea; ea = eb; eb = t;
     }
