@@ -108,9 +108,12 @@ int dnpeff_set_csr_device(dnpeff_engine* eng, int64_t n_rows, int64_t n_cols_ful
 int dnpeff_get_shape(dnpeff_engine* eng, int64_t* n_rows, int64_t* n_cols_kept,
                      int64_t* col_start, int64_t* n_cols_shard, int64_t* nnz_shard);
 /* How the engine laid the shard out internally (no reference counterpart;
- * reported by the benchmark): columns held by at least 1/8 of the rows are
- * "popular" and go through the shared-memory tiled SpMM kernel, the rest is cut
- * into column blocks whose slice of H stays L2-resident while it is gathered. */
+ * reported by the benchmark): columns held by a sizeable share of the rows are
+ * "popular"; that block of A is kept a second time as a dense matrix and its part
+ * of both products runs on the tensor cores (ranks 32..128, multiples of 32;
+ * tile_rows = 0 then) or, for other ranks, through the shared-memory tiled SpMM
+ * kernel (tile_rows = rows of the dense factor per tile).  The rest is cut into
+ * column blocks whose slice of H stays L2-resident while it is gathered. */
 int dnpeff_get_layout(dnpeff_engine* eng, int64_t* n_popular_cols, int64_t* popular_nnz,
                       int32_t* n_tail_blocks, int32_t* tile_rows);
 /* newToOgIndex of removeSmallestL0NormColumns_inPlace: n_cols_kept original ids. */

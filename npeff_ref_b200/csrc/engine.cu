@@ -125,6 +125,14 @@ struct dnpeff_engine {
     std::vector<int64_t> tail_nnz;  // stored entries per tail block
     int* work_counter = nullptr;
     int* d_err = nullptr;
+    // Popular block of A kept dense for the tensor-core product (null: the popular
+    // part goes through the tiled sparse kernel): x1 = rows x popular columns,
+    // x2 = its transpose, both in the blocked layout of k_block_tc.
+    float* x1 = nullptr;
+    float* x2 = nullptr;
+    BlockTcPlan plan_x1 = {}, plan_x2 = {};
+    float* blk_ysplit = nullptr;
+    float* blk_partial = nullptr;
 
     float* W = nullptr;
     float* H = nullptr;
@@ -210,6 +218,15 @@ bool tensor_cores_enabled() {
     return v == 1;
 }
 
+// Popular columns hold at least ceil(n / div) entries.  With the dense tensor-core
+// block a column pays off from a few percent of density on; the sparse tiled
+// kernel needs longer columns.  DNPEFF_HOT_DIV overrides (experiments).
+int hot_divisor(bool dense) {
+    const char* s = getenv("DNPEFF_HOT_DIV");
+    if (s && atoi(s) >= 2) return atoi(s);
+    return dense ? 16 : 8;
+}
+
 // G = X^T X: tcgen05 kernel where the rank allows, CUDA-core kernel otherwise.
 int gram_any(const float* X, int64_t rows, int r, float* G, float* scratch, int* err, cudaStream_t st) {
     if (tensor_cores_enabled() && gram_tc_ok(r)) return gram_tc_launch(X, rows, r, G, scratch, err, st);
@@ -236,6 +253,7 @@ void free_matrix(dnpeff_engine* e) {
     dev_free(e->new_to_og);
     dev_free(e->perm); dev_free(e->inv_perm);
     dev_free(e->b_vals); dev_free(e->b_col); dev_free(e->tail_off);
+    dev_free(e->x1); dev_free(e->x2); dev_free(e->blk_ysplit); dev_free(e->blk_partial);
     e->tail_nnz.clear();
     e->n_hot = 0; e->n_tail_blocks = 0;
     dev_free(e->W); dev_free(e->H); dev_free(e->AHG); dev_free(e->WA); dev_free(e->WW);
@@ -380,8 +398,9 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_LAUNCH_CHECK();
     DN_COUNT_LAUNCH(1);
     const bool fast = spmm_fast_rank(r);
-    const int tile = fast ? spmm_tile_rows(r) : 128;
-    int32_t hot_thr = (int32_t)std::max<int64_t>(2, ceil_div(n, 8));
+    bool dense = fast && tensor_cores_enabled() && block_tc_ok(r);
+    int tile = fast ? spmm_tile_rows(r) : 128;
+    int32_t hot_thr = (int32_t)std::max<int64_t>(2, ceil_div(n, hot_divisor(dense)));
     if (!fast || n < 32) hot_thr = INT32_MAX;  // no hot part
     DN_TRY(hot_flags.alloc((size_t)ms + 1));
     DN_TRY(hot_pos.alloc((size_t)ms + 1));
@@ -392,7 +411,19 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     int64_t n_hot = 0;
     DN_CUDA(cudaMemcpyAsync(&n_hot, hot_pos.p + ms, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
     DN_CUDA(cudaStreamSynchronize(st));
-    const int64_t max_hot = (int64_t)kMaxHotTiles * tile;
+    int64_t max_hot = (int64_t)kMaxHotTiles * tile;
+    if (dense) {
+        // both dense copies (8 bytes per element of the block) within a third of
+        // the memory that is free now
+        size_t free_b = 0, total_b = 0;
+        DN_CUDA(cudaMemGetInfo(&free_b, &total_b));
+        max_hot = (int64_t)(free_b / 3 / (8 * (size_t)std::max<int64_t>(n, 1)));
+        max_hot = std::min<int64_t>(max_hot / 128 * 128, (int64_t)1 << 21);
+        if (max_hot < 128) {
+            dense = false;
+            max_hot = (int64_t)kMaxHotTiles * tile;
+        }
+    }
     if (n_hot > max_hot || n_hot < 8) {
         // too many (cap the tile loop) or too few to be worth a launch: raise the
         // bar until the count fits, or drop the hot part
@@ -440,6 +471,8 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             nb = ceil_div(tail_cols, block);
         }
         if (tail_cols <= 0) nb = 0;
+        if (n_hot <= 0) dense = false;
+        if (dense) tile = (int)std::max<int64_t>(n_hot, 1);  // the dense block needs no tiles: one hot bucket
         BucketMap bm;
         bm.n_hot = n_hot;
         bm.tile = tile;
@@ -457,6 +490,24 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 16);
             k_bucket_rows<<<(unsigned)blocks, 256, smem, st>>>(e->a_vals, e->a_col, e->a_rowptr, n, e->inv_perm,
                                                               bm, e->b_vals, e->b_col, e->tail_off);
+            DN_LAUNCH_CHECK();
+            DN_COUNT_LAUNCH(1);
+        }
+        if (dense) {
+            e->plan_x1 = block_tc_plan(n, n_hot, r);
+            e->plan_x2 = block_tc_plan(n_hot, n, r);
+            DN_CUDA(cudaMalloc((void**)&e->x1, sizeof(float) * e->plan_x1.x_floats));
+            DN_CUDA(cudaMalloc((void**)&e->x2, sizeof(float) * e->plan_x2.x_floats));
+            DN_CUDA(cudaMalloc((void**)&e->blk_ysplit,
+                               sizeof(float) * std::max(e->plan_x1.ysplit_floats, e->plan_x2.ysplit_floats)));
+            DN_CUDA(cudaMalloc((void**)&e->blk_partial,
+                               sizeof(float) * std::max(e->plan_x1.partial_floats, e->plan_x2.partial_floats)));
+            DN_CUDA(cudaMemsetAsync(e->x1, 0, sizeof(float) * e->plan_x1.x_floats, st));
+            DN_CUDA(cudaMemsetAsync(e->x2, 0, sizeof(float) * e->plan_x2.x_floats, st));
+            int64_t blocks = std::min<int64_t>(ceil_div(n, 8), (int64_t)kNumSMs * 16);
+            k_fill_blocks<<<(unsigned)blocks, 256, 0, st>>>(e->b_vals, e->b_col, e->a_rowptr, e->tail_off,
+                                                           (int)(nb + 1), n, e->plan_x1.k_chunks,
+                                                           e->plan_x2.k_chunks, e->x1, e->x2);
             DN_LAUNCH_CHECK();
             DN_COUNT_LAUNCH(1);
         }
@@ -567,7 +618,12 @@ int spmm_ah(dnpeff_engine* e, float* AH) {
     if (e->n <= 0) return DNPEFF_OK;
     int accumulate = 0;
     const int stride = e->n_tail_blocks + 1;
-    if (e->n_hot > 0) {
+    if (e->x1) {
+        // popular block on the tensor cores: AH = A_pop * H_pop (H's first n_hot rows)
+        DN_TRY(block_tc_launch(e->x1, e->plan_x1, e->H, e->n, e->n_hot, r, AH, e->blk_ysplit, e->blk_partial,
+                               e->d_err, e->st));
+        accumulate = 1;
+    } else if (e->n_hot > 0) {
         SpmmCall c;
         c.kind = kSpmmTiled;
         c.vals = e->b_vals; c.ind = e->b_col;
@@ -599,7 +655,11 @@ int spmm_wa(dnpeff_engine* e) {
     const int r = e->p.rank;
     if (!spmm_fast_rank(r))
         return spmm_dispatch(e->c_vals, e->c_row, e->c_colptr, e->ms, e->W, r, e->WA, e->plan_csc, e->st);
-    if (e->n_hot > 0) {
+    if (e->x2) {
+        // popular columns on the tensor cores: WA[0, n_hot) = A_pop^T * W
+        DN_TRY(block_tc_launch(e->x2, e->plan_x2, e->W, e->n_hot, e->n, r, e->WA, e->blk_ysplit, e->blk_partial,
+                               e->d_err, e->st));
+    } else if (e->n_hot > 0) {
         SpmmCall c;
         c.kind = kSpmmTiled;
         c.vals = e->c_vals; c.ind = e->c_row;
@@ -931,7 +991,7 @@ int dnpeff_get_layout(dnpeff_engine* e, int64_t* n_hot_cols, int64_t* hot_nnz, i
     if (n_hot_cols) *n_hot_cols = e->n_hot;
     if (hot_nnz) *hot_nnz = v;
     if (n_tail_blocks) *n_tail_blocks = e->n_tail_blocks;
-    if (tile_rows) *tile_rows = e->bm.tile;
+    if (tile_rows) *tile_rows = e->x1 ? 0 : e->bm.tile;
     return DNPEFF_OK;
 }
 

@@ -277,6 +277,37 @@ def test_full_run_matches_oracle(torch_cuda, n, m, k, r, iters, eps):
         assert W.min() >= 0 and H.min() >= 0
 
 
+def test_popular_block_is_dense_and_matches_oracle(torch_cuda):
+    """Ranks 32..128 (multiples of 32) keep the popular columns as a dense block
+    for the tensor-core kernel (layout reports tile_rows == 0): several row tiles
+    and K splits, one half step each way against the oracle."""
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k, r, eps = 700, 20000, 2000, 64, 1e-12
+    vals, idx, norms = make_problem(n, m, k, seed=123)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    scale = baseline_scale(v, n, mk, r)
+    with _engine(MuNmfParams(rank=r, eps=eps, seed=2, init_scale=scale)) as eng:
+        eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+        n_pop, pop_nnz, n_blocks, tile_rows = eng.layout()
+        assert n_pop > 128 and pop_nnz > 0 and tile_rows == 0
+        eng.init_factors()
+        W0, H0 = eng.load_w_to_host(), eng.load_h_to_host()
+        eng.step_w()
+        W1 = eng.load_w_to_host()
+        assert rel_fro(W1, O.step_w(v, c, rp, mk, W0, H0, eps)) < 2e-6
+        eng.step_h()
+        H1 = eng.load_h_to_host()
+        Ho1 = O.step_h(v, c, rp, mk, W1, H0, eps)
+        assert rel_fro(H1, Ho1) < 2e-6
+        # element-wise too: a popular column must not differ from a tail column in accuracy
+        assert np.max(np.abs(H1 - Ho1) / (np.abs(Ho1) + 1e-30)) < 1e-4
+    # a rank outside the tensor-core set keeps the sparse tiled kernel
+    with _engine(MuNmfParams(rank=48, eps=eps, seed=2, init_scale=scale)) as eng:
+        eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+        assert eng.layout()[3] > 0
+
+
 def test_run_is_repeatable_bit_for_bit(torch_cuda):
     from npeff_ref_b200 import MuNmfParams
     n, m, k, r = 128, 4000, 1200, 64
