@@ -220,11 +220,16 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--scale-rows", type=float, default=1.0,
                     help="shrink n (profiling captures on a small case); not a bench value")
+    ap.add_argument("--scale-cols", type=float, default=1.0,
+                    help="shrink m and k alike (profiling captures on a small case); not a bench value")
     args = ap.parse_args()
     cfg_id = args.config
     c = dict(CONFIGS[cfg_id])
     if args.scale_rows != 1.0:
         c["n"] = max(1, int(c["n"] * args.scale_rows))
+    if args.scale_cols != 1.0:
+        c["m"] = max(1, int(c["m"] * args.scale_cols))
+        c["k"] = max(1, min(c["m"], int(c["k"] * args.scale_cols)))
     if args.impl == "reference":
         return run_reference_arm(args, c, cfg_id)
 
