@@ -102,6 +102,16 @@ int dnpeff_set_csr_device(dnpeff_engine* eng, int64_t n_rows, int64_t n_cols_ful
                           const int32_t* d_colind, const float* d_norms,
                           int32_t min_values_per_parameter);
 
+/* The same loader with the kept columns given as a list of original column ids
+ * instead of a count threshold: CsrMatrix::RetainColumns_InPlace
+ * (src/cuda/host/sparse_matrix.h:141-170) as fit_coeffs_to_sparse_H applies it
+ * with a decomposition's reduce_kept_indices (mains/fit_coeffs_to_sparse_H.cu:
+ * 137-140).  A column's new index is its position in the list; entries in other
+ * columns are dropped; an id listed twice keeps its last position. */
+int dnpeff_set_csr_retain(dnpeff_engine* eng, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
+                          const int64_t* rowptr, const float* vals, const int32_t* colind,
+                          const float* norms, const int32_t* retained_cols, int64_t n_retained);
+
 /* Shapes after the loader ran.  n_cols_kept = columns surviving the pruning
  * (over all shards); this engine owns kept columns [col_start, col_start+n_cols_shard)
  * (getSizeOfSplit, src/util/matrix_util.h:10-20). */
@@ -160,6 +170,20 @@ int dnpeff_save_decomposition_hdf5(const char* path, const float* W, const float
 int dnpeff_decomposition_hdf5_info(const char* path, int64_t* n_examples, int32_t* rank,
                                    int64_t* n_kept, int64_t* full_dense_size);
 int dnpeff_read_decomposition_hdf5(const char* path, float* W, float* H, int32_t* reduce_kept_indices);
+/* Decomposition with H in CSR form (SparseNmfDecomposition::save / ::read,
+ * src/io/nmf_decomp_h5.h:134-237; scripts/sparsify_d_npeff.py:27-73 writes the
+ * same file): data/W, data/H/{values, row_indices, column_indices} with the
+ * attribute data/H.shape = {rank, n_kept}, data/reduce_kept_indices with the
+ * attribute full_dense_size.  Row offsets are written as int64, column ids as
+ * int32 (the script's types); any integer width is read.  Outputs may be NULL. */
+int dnpeff_save_sparse_decomposition_hdf5(const char* path, const float* W, int64_t n_examples, int32_t rank,
+                                          const int64_t* h_rowptr, const int32_t* h_colind,
+                                          const float* h_vals, const int32_t* reduce_kept_indices,
+                                          int64_t n_kept, int64_t full_dense_size);
+int dnpeff_sparse_decomposition_hdf5_info(const char* path, int64_t* n_examples, int32_t* rank,
+                                          int64_t* n_kept, int64_t* h_nnz, int64_t* full_dense_size);
+int dnpeff_read_sparse_decomposition_hdf5(const char* path, float* W, int64_t* h_rowptr, int32_t* h_colind,
+                                          float* h_vals, int32_t* reduce_kept_indices);
 /* Shape/type of any dataset, and its leading rows x cols block as float64
  * (src/util/h5_util.h helpers). */
 int dnpeff_hdf5_dataset_info(const char* path, const char* dataset, int32_t* rank, int64_t dims[4],
@@ -173,6 +197,19 @@ int dnpeff_hdf5_read_f64(const char* path, const char* dataset, int64_t rows, in
  * "generate": init_scale * U(0,1] from a counter-based hash of (seed, global
  * element index), identical on every shard layout and reproducible on a CPU. */
 int dnpeff_init_factors(dnpeff_engine* eng, const float* W, const float* H);
+/* H from its CSR form (rank rows x n_cols_kept columns; int64 row offsets, int32
+ * column ids, as the sparse decomposition file holds them, src/io/nmf_decomp_h5.h:
+ * 134-170): zero elsewhere.  The engine keeps H dense (the sparse-sparse products
+ * of Nmf::OnlyW::SparseH::Learner, src/nmf/sparse2/nmf_sparse_H.h:157-166,
+ * 252-262, become the engine's A*H^T and H*H^T); on a sharded engine entries of
+ * other shards' columns are skipped.  W is generated if no factors were set yet. */
+int dnpeff_set_h_csr(dnpeff_engine* eng, const int64_t* h_rowptr, const int32_t* h_colind,
+                     const float* h_vals);
+/* Global index of the engine's first row, used only where W is generated: the
+ * row chunks of one matrix (SplitRowWise, src/cuda/host/sparse_matrix.h:219-245,
+ * as fit_coeffs_to_sparse_H feeds them) then draw the rows an unchunked engine
+ * would.  No reference counterpart (its generator is cuRAND over the whole W). */
+int dnpeff_set_w_row_offset(dnpeff_engine* eng, int64_t first_row);
 int dnpeff_set_init_scale(dnpeff_engine* eng, float init_scale);
 /* loadWToHostSync / loadHToHostSync + toRowMajor_inPlace
  * (multi_mu_dense_factors_nmf1.h:207-240, src/util/matrices.h:49-62). */

@@ -38,6 +38,7 @@ SIGNATURES = {
     "dnpeff_destroy": (C.c_int, [_P]),
     "dnpeff_set_csr": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_set_csr_device": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
+    "dnpeff_set_csr_retain": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "dnpeff_get_shape": (C.c_int, [_P] + [C.POINTER(_I64)] * 5),
     "dnpeff_get_layout": (C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I32), C.POINTER(_I32)]),
     "dnpeff_get_new_to_og": (C.c_int, [_P, _P]),
@@ -47,6 +48,8 @@ SIGNATURES = {
     "dnpeff_a_sq_norm": (C.c_int, [_P, C.POINTER(C.c_double)]),
     "dnpeff_a_sum": (C.c_int, [_P, C.POINTER(C.c_double)]),
     "dnpeff_init_factors": (C.c_int, [_P, _P, _P]),
+    "dnpeff_set_h_csr": (C.c_int, [_P, _P, _P, _P]),
+    "dnpeff_set_w_row_offset": (C.c_int, [_P, _I64]),
     "dnpeff_set_init_scale": (C.c_int, [_P, C.c_float]),
     "dnpeff_get_w": (C.c_int, [_P, _P]),
     "dnpeff_get_h": (C.c_int, [_P, _P]),
@@ -71,6 +74,9 @@ SIGNATURES = {
     "dnpeff_decomposition_hdf5_info": (C.c_int, [C.c_char_p, C.POINTER(_I64), C.POINTER(_I32),
                                                  C.POINTER(_I64), C.POINTER(_I64)]),
     "dnpeff_read_decomposition_hdf5": (C.c_int, [C.c_char_p, _P, _P, _P]),
+    "dnpeff_save_sparse_decomposition_hdf5": (C.c_int, [C.c_char_p, _P, _I64, _I32, _P, _P, _P, _P, _I64, _I64]),
+    "dnpeff_sparse_decomposition_hdf5_info": (C.c_int, [C.c_char_p, _P, _P, _P, _P, _P]),
+    "dnpeff_read_sparse_decomposition_hdf5": (C.c_int, [C.c_char_p, _P, _P, _P, _P, _P]),
     "dnpeff_hdf5_dataset_info": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(_I32), C.POINTER(_I64),
                                            C.POINTER(_I32), C.POINTER(_I32)]),
     "dnpeff_hdf5_read_f64": (C.c_int, [C.c_char_p, C.c_char_p, _I64, _I64, _P]),

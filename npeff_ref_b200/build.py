@@ -12,6 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdnpeff.so")
 CLI = os.path.join(HERE, "bin", "run_nmf_on_pefs")
+CLI_FIT = os.path.join(HERE, "bin", "fit_coeffs_to_sparse_H")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -38,18 +39,19 @@ def needs_build():
 
 
 def build_cli():
-    """The `run_nmf_on_pefs` executable: plain C++ over the C ABI."""
+    """The `run_nmf_on_pefs` and `fit_coeffs_to_sparse_H` executables: plain C++ over the C ABI."""
     os.makedirs(os.path.dirname(CLI), exist_ok=True)
-    cmd = ["g++", "-O2", "-std=c++17", "-o", CLI, os.path.join(CSRC, "run_nmf_on_pefs.cpp"),
-           "-L" + HERE, "-ldnpeff", "-Wl,-rpath,$ORIGIN/..", "-lpthread"]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    for exe, src in ((CLI, "run_nmf_on_pefs.cpp"), (CLI_FIT, "fit_coeffs_to_sparse_H.cpp")):
+        cmd = ["g++", "-O2", "-std=c++17", "-o", exe, os.path.join(CSRC, src),
+               "-L" + HERE, "-ldnpeff", "-Wl,-rpath,$ORIGIN/..", "-lpthread"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
     return CLI
 
 
 def build(force=False, verbose=False):
-    if not force and not needs_build() and os.path.exists(CLI):
+    if not force and not needs_build() and os.path.exists(CLI) and os.path.exists(CLI_FIT):
         return LIB
     cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
         ["-o", LIB] + _sources() + ["-ldl"]

@@ -148,6 +148,7 @@ struct dnpeff_engine {
 
     double a_sq = 0.0, a_sum = 0.0;
     double a_sq_global = -1.0;
+    int64_t w_row_offset = 0;  // global index of this engine's first row (generated W only)
 
     ncclComm_t comm = nullptr;
     int comm_rank = 0, comm_size = 1;
@@ -288,8 +289,11 @@ void shard_range(int64_t total, int n_shards, int idx, int64_t* start, int64_t* 
     *size = (idx == n_shards - 1) ? base + total % n_shards : base;
 }
 
+// d_retained != nullptr: the kept columns are that list of original ids (device
+// pointer, n_retained of them) instead of the columns with >= min_count entries.
 int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const int64_t* d_rowptr,
-                const float* d_vals, const int32_t* d_col, const float* d_norms, int32_t min_count) {
+                const float* d_vals, const int32_t* d_col, const float* d_norms, int32_t min_count,
+                const int32_t* d_retained = nullptr, int64_t n_retained = 0) {
     if (n < 0 || m_full < 0 || (d_rowptr == nullptr && k < 0))
         return fail(DNPEFF_ERR_INVALID, "negative shape");
     if (n >= INT32_MAX || m_full >= INT32_MAX)
@@ -326,25 +330,40 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_TRY(read_err_flag(err.p, st, &herr));
     if (herr) return data_error(herr);
 
-    // 2. keep mask -> ascending renumbering
-    DN_TRY(flags.alloc_zero((size_t)m_full + 1, st));
-    DN_TRY(pos.alloc((size_t)m_full + 1));
+    // 2. keep mask -> ascending renumbering, or the caller's list of kept columns
     DN_TRY(og_to_new.alloc((size_t)m_full + 1));
-    if (m_full > 0) {
-        k_keep_flags<<<(unsigned)ceil_div(m_full, 256), 256, 0, st>>>(counts.p, m_full, min_count, flags.p);
-        DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(1);
-    }
-    DN_TRY(scan_exclusive<int32_t>(flags.p, pos.p, m_full + 1, st));
     int64_t m_kept = 0;
-    DN_CUDA(cudaMemcpyAsync(&m_kept, pos.p + m_full, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-    DN_CUDA(cudaStreamSynchronize(st));
-    DN_CUDA(cudaMalloc((void**)&e->new_to_og, sizeof(int32_t) * (size_t)std::max<int64_t>(m_kept, 1)));
-    if (m_full > 0) {
-        k_build_maps<<<(unsigned)ceil_div(m_full, 256), 256, 0, st>>>(flags.p, pos.p, m_full,
-                                                                     og_to_new.p, e->new_to_og);
-        DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(1);
+    if (d_retained) {
+        if (n_retained < 0 || n_retained >= INT32_MAX) return fail(DNPEFF_ERR_INVALID, "bad retained-column count");
+        m_kept = n_retained;
+        DN_CUDA(cudaMalloc((void**)&e->new_to_og, sizeof(int32_t) * (size_t)std::max<int64_t>(m_kept, 1)));
+        DN_CUDA(cudaMemsetAsync(og_to_new.p, 0xFF, sizeof(int32_t) * ((size_t)m_full + 1), st));
+        if (m_kept > 0) {
+            k_retain_maps<<<(unsigned)ceil_div(m_kept, 256), 256, 0, st>>>(d_retained, m_kept, m_full, og_to_new.p,
+                                                                          e->new_to_og, err.p);
+            DN_LAUNCH_CHECK();
+            DN_COUNT_LAUNCH(1);
+        }
+        DN_TRY(read_err_flag(err.p, st, &herr));
+        if (herr) return fail(DNPEFF_ERR_DATA, "retained column id outside [0, n_cols_full)");
+    } else {
+        DN_TRY(flags.alloc_zero((size_t)m_full + 1, st));
+        DN_TRY(pos.alloc((size_t)m_full + 1));
+        if (m_full > 0) {
+            k_keep_flags<<<(unsigned)ceil_div(m_full, 256), 256, 0, st>>>(counts.p, m_full, min_count, flags.p);
+            DN_LAUNCH_CHECK();
+            DN_COUNT_LAUNCH(1);
+        }
+        DN_TRY(scan_exclusive<int32_t>(flags.p, pos.p, m_full + 1, st));
+        DN_CUDA(cudaMemcpyAsync(&m_kept, pos.p + m_full, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+        DN_CUDA(cudaStreamSynchronize(st));
+        DN_CUDA(cudaMalloc((void**)&e->new_to_og, sizeof(int32_t) * (size_t)std::max<int64_t>(m_kept, 1)));
+        if (m_full > 0) {
+            k_build_maps<<<(unsigned)ceil_div(m_full, 256), 256, 0, st>>>(flags.p, pos.p, m_full,
+                                                                         og_to_new.p, e->new_to_og);
+            DN_LAUNCH_CHECK();
+            DN_COUNT_LAUNCH(1);
+        }
     }
 
     // 3. this engine's range of kept columns
@@ -764,7 +783,8 @@ int init_generated(dnpeff_engine* e, bool do_w, bool do_h) {
     const int r = e->p.rank;
     float scale = e->p.init_scale > 0.f ? e->p.init_scale : 1.0f;
     if (do_w && e->n > 0) {
-        k_init_uniform<<<kNumSMs * 8, 256, 0, e->st>>>(e->W, 0, e->n * r, stream_key(e->p.seed, 0), scale);
+        k_init_uniform<<<kNumSMs * 8, 256, 0, e->st>>>(e->W, e->w_row_offset * r, e->n * r,
+                                                       stream_key(e->p.seed, 0), scale);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
     }
@@ -936,9 +956,32 @@ int dnpeff_set_csr_device(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full,
     return s;
 }
 
+namespace {
+int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
+                 const int64_t* rowptr, const float* vals, const int32_t* colind, const float* norms,
+                 int32_t min_values_per_parameter, const int32_t* retained, int64_t n_retained);
+}
+
 int dnpeff_set_csr(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
                    const int64_t* rowptr, const float* vals, const int32_t* colind,
                    const float* norms, int32_t min_values_per_parameter) {
+    return set_csr_host(e, n_rows, n_cols_full, k_per_row, rowptr, vals, colind, norms,
+                        min_values_per_parameter, nullptr, 0);
+}
+
+int dnpeff_set_csr_retain(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
+                          const int64_t* rowptr, const float* vals, const int32_t* colind,
+                          const float* norms, const int32_t* retained_cols, int64_t n_retained) {
+    if (!retained_cols && n_retained > 0) return fail(DNPEFF_ERR_INVALID, "null retained_cols");
+    static const int32_t none = 0;
+    return set_csr_host(e, n_rows, n_cols_full, k_per_row, rowptr, vals, colind, norms, 1,
+                        retained_cols ? retained_cols : &none, n_retained);
+}
+
+namespace {
+int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
+                 const int64_t* rowptr, const float* vals, const int32_t* colind, const float* norms,
+                 int32_t min_values_per_parameter, const int32_t* retained, int64_t n_retained) {
     if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
     if (n_rows < 0) return fail(DNPEFF_ERR_INVALID, "negative shape");
     DeviceGuard g(e->device);
@@ -964,11 +1007,19 @@ int dnpeff_set_csr(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_
         if (n_rows > 0)
             DN_CUDA(cudaMemcpyAsync(dn.p, norms, sizeof(float) * (size_t)n_rows, cudaMemcpyHostToDevice, e->st));
     }
-    int s = dnpeff_set_csr_device(e, n_rows, n_cols_full, k_per_row, rowptr ? dr.p : nullptr, dv.p,
-                                  dc.p, norms ? dn.p : nullptr, min_values_per_parameter);
+    DevBuf<int32_t> dret;
+    if (retained) {
+        DN_TRY(dret.alloc((size_t)std::max<int64_t>(n_retained, 1)));
+        if (n_retained > 0)
+            DN_CUDA(cudaMemcpyAsync(dret.p, retained, sizeof(int32_t) * (size_t)n_retained, cudaMemcpyHostToDevice, e->st));
+    }
+    int s = load_device(e, n_rows, n_cols_full, k_per_row, rowptr ? dr.p : nullptr, dv.p, dc.p,
+                        norms ? dn.p : nullptr, min_values_per_parameter, retained ? dret.p : nullptr, n_retained);
+    if (s != DNPEFF_OK) free_matrix(e);
     cudaStreamSynchronize(e->st);
     return s;
 }
+}  // namespace
 
 int dnpeff_get_shape(dnpeff_engine* e, int64_t* n_rows, int64_t* n_cols_kept, int64_t* col_start,
                      int64_t* n_cols_shard, int64_t* nnz_shard) {
@@ -1098,6 +1149,50 @@ int dnpeff_init_factors(dnpeff_engine* e, const float* W, const float* H) {
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(2);
         DN_CUDA(cudaStreamSynchronize(e->st));
+    }
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    e->have_factors = true;
+    return DNPEFF_OK;
+}
+
+int dnpeff_set_w_row_offset(dnpeff_engine* e, int64_t first_row) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    if (first_row < 0) return fail(DNPEFF_ERR_INVALID, "negative row offset");
+    e->w_row_offset = first_row;
+    return DNPEFF_OK;
+}
+
+int dnpeff_set_h_csr(dnpeff_engine* e, const int64_t* h_rowptr, const int32_t* h_colind, const float* h_vals) {
+    DN_TRY(check_ready(e, false));
+    if (!h_rowptr) return fail(DNPEFF_ERR_INVALID, "null h_rowptr");
+    DeviceGuard g(e->device);
+    const int r = e->p.rank;
+    const int64_t nnz = h_rowptr[r];
+    if (h_rowptr[0] != 0 || nnz < 0) return fail(DNPEFF_ERR_DATA, "row offsets of H must start at 0");
+    for (int t = 0; t < r; t++)
+        if (h_rowptr[t + 1] < h_rowptr[t]) return fail(DNPEFF_ERR_DATA, "row offsets of H are not non-decreasing");
+    if (nnz > 0 && (!h_colind || !h_vals)) return fail(DNPEFF_ERR_INVALID, "null column ids / values of H");
+    if (!e->have_factors) DN_TRY(init_generated(e, true, false));  // W as dnpeff_init_factors(NULL, .) makes it
+    DN_CUDA(cudaMemsetAsync(e->H, 0, sizeof(float) * (size_t)std::max<int64_t>(e->ms * r, 1), e->st));
+    if (nnz > 0 && e->ms > 0) {
+        DevBuf<int64_t> drp;
+        DevBuf<int32_t> dc;
+        DevBuf<float> dv;
+        DevBuf<int> err;
+        DN_TRY(drp.alloc((size_t)r + 1));
+        DN_TRY(dc.alloc((size_t)nnz));
+        DN_TRY(dv.alloc((size_t)nnz));
+        DN_TRY(err.alloc_zero(1, e->st));
+        DN_CUDA(cudaMemcpyAsync(drp.p, h_rowptr, sizeof(int64_t) * (size_t)(r + 1), cudaMemcpyHostToDevice, e->st));
+        DN_CUDA(cudaMemcpyAsync(dc.p, h_colind, sizeof(int32_t) * (size_t)nnz, cudaMemcpyHostToDevice, e->st));
+        DN_CUDA(cudaMemcpyAsync(dv.p, h_vals, sizeof(float) * (size_t)nnz, cudaMemcpyHostToDevice, e->st));
+        k_scatter_h_csr<<<(unsigned)ceil_div(nnz, 256), 256, 0, e->st>>>(drp.p, dc.p, dv.p, r, nnz, e->m_kept, e->map,
+                                                                         e->inv_perm, e->H, err.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+        int herr = 0;
+        DN_TRY(read_err_flag(err.p, e->st, &herr));
+        if (herr) return fail(DNPEFF_ERR_DATA, "a column id of H is outside [0, n_cols_kept)");
     }
     DN_CUDA(cudaStreamSynchronize(e->st));
     e->have_factors = true;

@@ -158,6 +158,97 @@ int dnpeff_read_decomposition_hdf5(const char* path, float* W, float* H, int32_t
     return DNPEFF_OK;
 }
 
+// ---- decomposition with H in CSR form (SparseNmfDecomposition, src/io/nmf_decomp_h5.h:134-237;
+// written by scripts/sparsify_d_npeff.py:27-73 with int64 row offsets and int32 column ids) ----
+int dnpeff_save_sparse_decomposition_hdf5(const char* path, const float* W, int64_t n_examples, int32_t rank,
+                                          const int64_t* h_rowptr, const int32_t* h_colind, const float* h_vals,
+                                          const int32_t* reduce_kept_indices, int64_t n_kept,
+                                          int64_t full_dense_size) {
+    if (!path || !W || !h_rowptr || (!reduce_kept_indices && n_kept > 0))
+        return fail(DNPEFF_ERR_INVALID, "null argument");
+    const int64_t nnz = h_rowptr[rank];
+    if (nnz < 0 || (nnz > 0 && (!h_colind || !h_vals))) return fail(DNPEFF_ERR_INVALID, "bad CSR arrays");
+    try {
+        h5lite::Writer w(path);
+        w.add_group("data");
+        w.add_dataset("data/W", h5lite::DType::f32(), {(uint64_t)n_examples, (uint64_t)rank}, W);
+        w.add_group("data/H");
+        float dummy_f = 0.f;
+        int32_t dummy_i = 0;
+        w.add_dataset("data/H/values", h5lite::DType::f32(), {(uint64_t)nnz}, nnz ? (const void*)h_vals : &dummy_f);
+        w.add_dataset("data/H/row_indices", h5lite::DType::i64(), {(uint64_t)rank + 1}, h_rowptr);
+        w.add_dataset("data/H/column_indices", h5lite::DType::i32(), {(uint64_t)nnz},
+                      nnz ? (const void*)h_colind : &dummy_i);
+        int64_t shape[2] = {rank, n_kept};
+        w.add_attr("data/H", "shape", h5lite::DType::i64(), {2}, shape);
+        w.add_dataset("data/reduce_kept_indices", h5lite::DType::i32(), {(uint64_t)n_kept},
+                      n_kept ? (const void*)reduce_kept_indices : &dummy_i);
+        int32_t fds = (int32_t)full_dense_size;
+        w.add_attr("data/reduce_kept_indices", "full_dense_size", h5lite::DType::i32(), {1}, &fds);
+        w.finish();
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_sparse_decomposition_hdf5_info(const char* path, int64_t* n_examples, int32_t* rank, int64_t* n_kept,
+                                          int64_t* h_nnz, int64_t* full_dense_size) {
+    if (!path) return fail(DNPEFF_ERR_INVALID, "null path");
+    try {
+        h5lite::Reader rd(path);
+        h5lite::ObjectInfo W = rd.dataset("data/W"), V = rd.dataset("data/H/values");
+        h5lite::ObjectInfo R = rd.dataset("data/H/row_indices"), C = rd.dataset("data/H/column_indices");
+        h5lite::ObjectInfo K = rd.dataset("data/reduce_kept_indices");
+        std::vector<int64_t> shape = rd.attr_ints(rd.object(rd.find("data/H")), "shape");
+        if (W.space.dims.size() != 2 || shape.size() != 2 || V.space.dims.size() != 1 || R.space.dims.size() != 1 ||
+            C.space.dims.size() != 1)
+            return fail(DNPEFF_ERR_IO, "not a sparse decomposition file");
+        if ((int64_t)W.space.dims[1] != shape[0] || (int64_t)R.space.dims[0] != shape[0] + 1 ||
+            V.space.dims[0] != C.space.dims[0] || K.space.count() != (uint64_t)shape[1])
+            return fail(DNPEFF_ERR_IO, "data/W, data/H and data/reduce_kept_indices do not agree in shape");
+        if (n_examples) *n_examples = (int64_t)W.space.dims[0];
+        if (rank) *rank = (int32_t)shape[0];
+        if (n_kept) *n_kept = shape[1];
+        if (h_nnz) *h_nnz = (int64_t)V.space.dims[0];
+        if (full_dense_size) *full_dense_size = rd.attr_int(K, "full_dense_size");
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
+int dnpeff_read_sparse_decomposition_hdf5(const char* path, float* W, int64_t* h_rowptr, int32_t* h_colind,
+                                          float* h_vals, int32_t* reduce_kept_indices) {
+    if (!path) return fail(DNPEFF_ERR_INVALID, "null path");
+    try {
+        h5lite::Reader rd(path);
+        if (W) {
+            h5lite::ObjectInfo o = rd.dataset("data/W");
+            rd.read_leading(o, o.space.dims[0], o.space.dims[1], h5lite::DType::f32(), W);
+        }
+        if (h_rowptr) {
+            h5lite::ObjectInfo o = rd.dataset("data/H/row_indices");
+            rd.read_leading(o, o.space.dims[0], 1, h5lite::DType::i64(), h_rowptr);
+        }
+        if (h_colind) {
+            h5lite::ObjectInfo o = rd.dataset("data/H/column_indices");
+            if (o.space.count() > 0) rd.read_leading(o, o.space.dims[0], 1, h5lite::DType::i32(), h_colind);
+        }
+        if (h_vals) {
+            h5lite::ObjectInfo o = rd.dataset("data/H/values");
+            if (o.space.count() > 0) rd.read_leading(o, o.space.dims[0], 1, h5lite::DType::f32(), h_vals);
+        }
+        if (reduce_kept_indices) {
+            h5lite::ObjectInfo o = rd.dataset("data/reduce_kept_indices");
+            if (o.space.count() > 0) rd.read_leading(o, o.space.dims[0], 1, h5lite::DType::i32(), reduce_kept_indices);
+        }
+    } catch (const std::exception& ex) {
+        return fail(DNPEFF_ERR_IO, "%s", ex.what());
+    }
+    return DNPEFF_OK;
+}
+
 // Generic probe used by the tests: shape and type of any dataset.
 int dnpeff_hdf5_dataset_info(const char* path, const char* dataset, int32_t* rank, int64_t dims[4],
                              int32_t* is_float, int32_t* type_size) {

@@ -571,6 +571,16 @@ class Reader {
         return v;
     }
 
+    // All elements of an integer (or float) attribute, converted to int64.
+    std::vector<int64_t> attr_ints(const ObjectInfo& o, const std::string& name) {
+        auto it = o.attrs.find(name);
+        if (it == o.attrs.end()) throw Error("h5lite: attribute '" + name + "' not found");
+        uint64_t count = it->second.space.count();
+        std::vector<int64_t> v((size_t)count, 0);
+        if (count > 0) convert(it->second.data.data(), it->second.type, (uint8_t*)v.data(), DType::i64(), count);
+        return v;
+    }
+
   private:
     std::string path_;
     FILE* f_ = nullptr;

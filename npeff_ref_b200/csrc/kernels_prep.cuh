@@ -120,6 +120,48 @@ __global__ void k_build_maps(const int32_t* __restrict__ flags, const int64_t* _
     }
 }
 
+// RetainColumns_InPlace (src/cuda/host/sparse_matrix.h:141-170): the kept columns
+// are a given list of original ids and a column's new index is its position in
+// the list (the last position wins if an id is listed twice, as in the sequential
+// loop there).  og_to_new must be filled with -1 before.
+__global__ void k_retain_maps(const int32_t* __restrict__ retained, int64_t n_retained, int64_t n_cols,
+                              int32_t* __restrict__ og_to_new, int32_t* __restrict__ new_to_og,
+                              int* __restrict__ err) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_retained) return;
+    int32_t c = retained[i];
+    new_to_og[i] = c;
+    if (c < 0 || c >= n_cols) {
+        atomicOr(err, kErrColRange);
+        return;
+    }
+    atomicMax(&og_to_new[c], (int32_t)i);
+}
+
+// H given in CSR form (rank rows x kept columns) scattered into this shard's dense
+// H (internal row order, zeroed before).  One thread per stored entry; an entry
+// whose column another shard owns is skipped.
+__global__ void k_scatter_h_csr(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
+                                const float* __restrict__ vals, int r, int64_t nnz, int64_t m_kept,
+                                ShardMap map, const int32_t* __restrict__ inv_perm, float* __restrict__ H,
+                                int* __restrict__ err) {
+    int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= nnz) return;
+    // the row of H that holds entry p: last t with rowptr[t] <= p
+    int lo = 0, hi = r;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (rowptr[mid] <= p) lo = mid; else hi = mid;
+    }
+    const int64_t c = colind[p];
+    if (c < 0 || c >= m_kept) {
+        atomicOr(err, kErrColRange);
+        return;
+    }
+    if (!map.owns(c)) return;
+    H[(int64_t)inv_perm[map.local(c)] * r + lo] = vals[p];
+}
+
 // Entries of each row that fall into kept columns [c0, c0+w) of this shard:
 // the counting pass of splitColumnWise (src/util/matrix_util.h:39-44) merged
 // with the pruning test (src/util/sparse_util.h:139).  One block per row.

@@ -80,6 +80,30 @@ class MuNmf:
                                    _ptr(rowptr), _ptr(vals), _ptr(colind), _ptr(norms),
                                    int(min_values_per_parameter)))
 
+    def set_csr_retain(self, n_rows, n_cols_full, vals, colind, retained_cols, rowptr=None, k_per_row=0,
+                       norms=None):
+        """As ``set_csr`` with the kept columns given as a list of original column ids
+        (``CsrMatrix::RetainColumns_InPlace``, src/cuda/host/sparse_matrix.h:141-170):
+        a column's new index is its position in the list."""
+        vals = np.ascontiguousarray(vals, dtype=np.float32).reshape(-1)
+        colind = np.ascontiguousarray(colind, dtype=np.int32).reshape(-1)
+        retained_cols = np.ascontiguousarray(retained_cols, dtype=np.int32).reshape(-1)
+        if rowptr is not None:
+            rowptr = np.ascontiguousarray(rowptr, dtype=np.int64)
+        if norms is not None:
+            norms = np.ascontiguousarray(norms, dtype=np.float32)
+        check(lib().dnpeff_set_csr_retain(self._h, int(n_rows), int(n_cols_full), int(k_per_row),
+                                          _ptr(rowptr), _ptr(vals), _ptr(colind), _ptr(norms),
+                                          _ptr(retained_cols), int(retained_cols.size)))
+
+    def set_h_csr(self, h_rowptr, h_colind, h_vals):
+        """H (rank x n_cols_kept) from CSR arrays; zero elsewhere (the sparse
+        decomposition file's form, src/io/nmf_decomp_h5.h:134-170)."""
+        h_rowptr = np.ascontiguousarray(h_rowptr, dtype=np.int64)
+        h_colind = np.ascontiguousarray(h_colind, dtype=np.int32)
+        h_vals = np.ascontiguousarray(h_vals, dtype=np.float32)
+        check(lib().dnpeff_set_h_csr(self._h, _ptr(h_rowptr), _ptr(h_colind), _ptr(h_vals)))
+
     def set_csr_device(self, n_rows, n_cols_full, d_vals, d_colind, d_rowptr=0, k_per_row=0,
                        d_norms=0, min_values_per_parameter=1):
         """Device pointers (ints), inputs already resident in HBM."""

@@ -112,6 +112,35 @@ def prune_columns(vals, colind, rowptr, n_cols, min_count=1):
     return vals[:q].copy(), colind[:q].copy(), rowptr, new_to_og[:kept].copy()
 
 
+def retain_columns(vals, colind, rowptr, n_cols, retained):
+    """CsrMatrix::RetainColumns_InPlace (src/cuda/host/sparse_matrix.h:141-170): keep
+    the entries whose column is in `retained`; a column's new index is its position
+    in that list (a later position overwrites an earlier one for a repeated id);
+    order inside a row is kept.  Returns (vals, colind, rowptr)."""
+    vals = np.asarray(vals, dtype=np.float32)
+    colind = np.asarray(colind)
+    rowptr = np.asarray(rowptr, dtype=np.int64)
+    old_to_new = np.full(int(n_cols), -1, dtype=np.int64)
+    for i, c in enumerate(np.asarray(retained)):      # sequential, as the reference loop
+        old_to_new[int(c)] = i
+    new = old_to_new[colind]
+    keep = new >= 0
+    rows = np.repeat(np.arange(len(rowptr) - 1), np.diff(rowptr))
+    out_ptr = np.zeros(len(rowptr), dtype=np.int64)
+    np.add.at(out_ptr, rows[keep] + 1, 1)
+    return vals[keep].copy(), new[keep].astype(np.int32), np.cumsum(out_ptr)
+
+
+def dense_to_csr(A, threshold):
+    """to_csr of scripts/sparsify_d_npeff.py:27-49: entries >= threshold, row by row;
+    int64 row offsets and int32 column ids as that script writes them."""
+    A = np.asarray(A)
+    mask = A >= threshold
+    rowptr = np.concatenate([[0], np.cumsum(mask.sum(axis=1))]).astype(np.int64)
+    cols = np.nonzero(mask)[1].astype(np.int32)
+    return A[mask].astype(np.float32), rowptr, cols
+
+
 def split_range(total, n_splits, idx):
     s, w = C.c_int64(0), C.c_int64(0)
     lib().oracle_split_range(C.c_int64(int(total)), C.c_int64(int(n_splits)), C.c_int64(int(idx)),

@@ -99,3 +99,74 @@ def test_cli_resume_from_initial_factor_files(tmp_path):
 def test_cli_missing_required_flag_aborts():
     res = subprocess.run([CLI, "--output_path=/tmp/x.h5"], capture_output=True, text=True)
     assert res.returncode != 0 and "Missing flag: per_example_fishers" in res.stdout
+
+
+CLI_FIT = os.path.join(ROOT, "npeff_ref_b200", "bin", "fit_coeffs_to_sparse_H")
+
+
+def _read_sparse(path):
+    a, b, c, d, e = C.c_int64(0), C.c_int32(0), C.c_int64(0), C.c_int64(0), C.c_int64(0)
+    check(lib().dnpeff_sparse_decomposition_hdf5_info(path.encode(), C.byref(a), C.byref(b), C.byref(c),
+                                                      C.byref(d), C.byref(e)))
+    W = np.empty((a.value, b.value), np.float32)
+    rp = np.empty(b.value + 1, np.int64)
+    ci = np.empty(max(d.value, 1), np.int32)
+    va = np.empty(max(d.value, 1), np.float32)
+    kept = np.empty(c.value, np.int32)
+    check(lib().dnpeff_read_sparse_decomposition_hdf5(
+        path.encode(), C.c_void_p(W.ctypes.data), C.c_void_p(rp.ctypes.data), C.c_void_p(ci.ctypes.data),
+        C.c_void_p(va.ctypes.data), C.c_void_p(kept.ctypes.data)))
+    return W, rp, ci[:d.value], va[:d.value], kept, e.value
+
+
+def test_fit_coeffs_cli_matches_oracle_and_is_chunk_invariant(tmp_path):
+    """fit_coeffs_to_sparse_H end to end (mains/fit_coeffs_to_sparse_H.cu): sparse
+    decomposition + new D-PEFs in, W for the new examples + the same sparse H out;
+    --n_row_splits_pefs must not change the result."""
+    n, m, k, r, iters = 150, 4000, 80, 12, 40
+    vals, idx, norms = make_problem(n, m, k, seed=71)
+    rng = np.random.default_rng(7)
+    kept = np.sort(rng.choice(np.unique(idx), 1200, replace=False)).astype(np.int32)
+    mk = len(kept)
+    Hd = (rng.random((r, mk), dtype=np.float32) * (rng.random((r, mk)) > 0.9)).astype(np.float32)
+    hv, hrp, hc = O.dense_to_csr(Hd, 1e-30)
+    W_old = rng.random((33, r), dtype=np.float32)            # the old examples' W is not used
+    pef, hpath = str(tmp_path / "pef.h5"), str(tmp_path / "sp.h5")
+    _write_pef(pef, vals, idx, norms, m)
+    check(lib().dnpeff_save_sparse_decomposition_hdf5(
+        hpath.encode(), C.c_void_p(W_old.ctypes.data), 33, r, C.c_void_p(hrp.ctypes.data),
+        C.c_void_p(hc.ctypes.data), C.c_void_p(hv.ctypes.data), C.c_void_p(kept.ctypes.data), mk, m))
+    outs = []
+    for splits in (1, 4):
+        out = str(tmp_path / ("out%d.h5" % splits))
+        res = subprocess.run([CLI_FIT, "--pef_path=" + pef, "--H_path=" + hpath, "--output_path=" + out,
+                              "--n_splits_sparse_matmul=2", "--n_row_splits_pefs=%d" % splits,
+                              "--nmf_max_iter=%d" % iters], capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, res.stdout + res.stderr
+        outs.append((_read_sparse(out), res.stdout))
+    (W, rp, ci, va, k2, dense), stdout = outs[0]
+    assert W.shape == (n, r) and dense == m
+    assert np.array_equal(rp, hrp) and np.array_equal(ci, hc) and np.array_equal(va, hv) and np.array_equal(k2, kept)
+    rowptr = np.arange(n + 1, dtype=np.int64) * k
+    nv = O.normalize_rows(vals.ravel(), rowptr, norms)
+    v, c, rpo = O.retain_columns(nv, idx.ravel(), rowptr, m, kept)
+    W0 = O.init_factors(n, mk, r, SEED, 1.0)[0]
+    Wo, lo = O.fit_w_only(v, c, rpo, mk, W0, Hd, iters, 1e-7)
+    assert rel_fro(W, Wo) < 1e-4
+    step = re.findall(r"^step (\d+): ([0-9.eE+-]+) \[", stdout, flags=re.M)
+    assert len(step) == 1 and int(step[0][0]) == iters and abs(float(step[0][1]) - lo) < 1e-4 * lo
+    # four row chunks: the same W (rows are independent given H; a chunk may order the
+    # sums of A*H^T differently, so equality is to rounding), the same loss
+    W4 = outs[1][0][0]
+    assert rel_fro(W4, W) < 1e-5
+    step4 = re.findall(r"^step (\d+): ([0-9.eE+-]+) \[", outs[1][1], flags=re.M)
+    assert abs(float(step4[0][1]) - lo) < 1e-4 * lo
+
+
+def test_fit_coeffs_cli_rejects_unknown_and_missing_flags(tmp_path):
+    res = subprocess.run([CLI_FIT, "--pef_path=x"], capture_output=True, text=True, timeout=60)
+    assert res.returncode != 0 and "Missing flag:" in res.stdout
+    res = subprocess.run([CLI_FIT, "--pef_path=x", "--H_path=y", "--output_path=z", "--n_splits_sparse_matmul=1",
+                          "--n_row_splits_pefs=1", "--nmf_max_iter=1", "--bogus=1"],
+                         capture_output=True, text=True, timeout=60)
+    assert res.returncode != 0 and "Unrecognized flags." in res.stdout

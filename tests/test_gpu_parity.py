@@ -415,3 +415,57 @@ def test_engine_matches_reference_engine_fixture(torch_cuda, path):
         assert rel_fro(eng.load_h_to_host(), g["H"]) < 1e-4
         l = eng.compute_uncached_loss()
         assert abs(l - float(g["loss"])) < 1e-3 * l   # the reference sums its loss terms in fp32
+
+
+def test_retain_columns_loader_bit_exact(torch_cuda):
+    """dnpeff_set_csr_retain against the oracle's RetainColumns_InPlace: an unsorted
+    list, a repeated id, ids that no row holds."""
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k = 90, 3000, 70
+    vals, idx, norms = make_problem(n, m, k, seed=17)
+    rowptr = np.arange(n + 1, dtype=np.int64) * k
+    nv = O.normalize_rows(vals.ravel(), rowptr, norms)
+    rng = np.random.default_rng(2)
+    used = np.unique(idx)
+    retained = rng.permutation(np.concatenate([rng.choice(used, 400, replace=False),
+                                               np.setdiff1d(np.arange(m), used)[:20]])).astype(np.int32)
+    retained = np.concatenate([retained, retained[:3]])        # three ids listed twice
+    ev, ec, erp = O.retain_columns(nv, idx.ravel(), rowptr, m, retained)
+    with _engine(MuNmfParams(rank=8)) as eng:
+        eng.set_csr_retain(n, m, vals, idx, retained, None, k, norms)
+        assert eng.shape[1] == len(retained)
+        assert np.array_equal(eng.new_to_og(), retained)
+        v, c, rp = eng.export_shard_csr()
+        assert np.array_equal(rp, erp) and np.array_equal(c, ec) and np.array_equal(v, ev)
+    with _engine(MuNmfParams(rank=8)) as eng:
+        with pytest.raises(Exception):
+            eng.set_csr_retain(n, m, vals, idx, np.array([5, m], np.int32), None, k, norms)
+
+
+@pytest.mark.parametrize("r", [16, 64])
+def test_fit_w_only_with_sparse_h_matches_oracle(torch_cuda, r):
+    """The fit_coeffs_to_sparse_H numerics (src/nmf/sparse2/nmf_sparse_H.h:116-127,
+    298-345): retained columns, H from CSR arrays, W-only updates with eps 1e-7."""
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k, iters, eps = 260, 5000, 120, 60, 1e-7
+    vals, idx, norms = make_problem(n, m, k, seed=90 + r)
+    rowptr = np.arange(n + 1, dtype=np.int64) * k
+    nv = O.normalize_rows(vals.ravel(), rowptr, norms)
+    rng = np.random.default_rng(r)
+    kept = np.sort(rng.choice(np.unique(idx), 1500, replace=False)).astype(np.int32)
+    mk = len(kept)
+    Hd = (rng.random((r, mk), dtype=np.float32) * (rng.random((r, mk)) > 0.93)).astype(np.float32)
+    hv, hrp, hc = O.dense_to_csr(Hd, 1e-30)
+    v, c, rp = O.retain_columns(nv, idx.ravel(), rowptr, m, kept)
+    with _engine(MuNmfParams(rank=r, eps=eps, seed=11, init_scale=0.5)) as eng:
+        eng.set_csr_retain(n, m, vals, idx, kept, None, k, norms)
+        eng.init_factors()
+        eng.set_h_csr(hrp, hc, hv)
+        W0 = eng.load_w_to_host()
+        assert np.array_equal(eng.load_h_to_host(), Hd)
+        assert np.array_equal(W0, O.init_factors(n, mk, r, 11, 0.5)[0])
+        loss = eng.fit_w_only(iters)
+        W = eng.load_w_to_host()
+    Wo, lo = O.fit_w_only(v, c, rp, mk, W0, Hd, iters, eps)
+    assert rel_fro(W, Wo) < 1e-4
+    assert abs(loss - lo) < 1e-5 * lo

@@ -138,3 +138,52 @@ def test_reader_parses_a_file_written_by_libhdf5():
     assert dims == (9, 1) and is_float and size == 8
     vals = _read(path, "testdouble", 9, 1).ravel()
     assert np.allclose(vals, np.arange(9) * np.pi / 4, rtol=0, atol=1e-15)   # MATLAB's 0:pi/4:2*pi
+
+
+def _sparse_info(path):
+    a, b, c, d, e = C.c_int64(0), C.c_int32(0), C.c_int64(0), C.c_int64(0), C.c_int64(0)
+    check(lib().dnpeff_sparse_decomposition_hdf5_info(path.encode(), C.byref(a), C.byref(b), C.byref(c),
+                                                      C.byref(d), C.byref(e)))
+    return a.value, b.value, c.value, d.value, e.value
+
+
+def test_sparse_decomposition_file_round_trip_and_layout(tmp_path):
+    """SparseNmfDecomposition::save / ::read (src/io/nmf_decomp_h5.h:134-237): W, H as
+    CSR under data/H with its shape attribute, reduce_kept_indices + full_dense_size."""
+    rng = np.random.default_rng(5)
+    n, r, m, dense = 17, 6, 53, 4000
+    W = rng.random((n, r), dtype=np.float32)
+    H = rng.random((r, m), dtype=np.float32)
+    H[H < 0.8] = 0
+    H[2] = 0                                               # an empty row
+    mask = H != 0
+    rowptr = np.concatenate([[0], np.cumsum(mask.sum(1))]).astype(np.int64)
+    cols = np.nonzero(mask)[1].astype(np.int32)
+    vals = H[mask].astype(np.float32)
+    kept = np.sort(rng.choice(dense, m, replace=False)).astype(np.int32)
+    path = str(tmp_path / "sp.h5")
+    check(lib().dnpeff_save_sparse_decomposition_hdf5(
+        path.encode(), C.c_void_p(W.ctypes.data), n, r, C.c_void_p(rowptr.ctypes.data),
+        C.c_void_p(cols.ctypes.data), C.c_void_p(vals.ctypes.data), C.c_void_p(kept.ctypes.data), m, dense))
+    assert _sparse_info(path) == (n, r, m, len(vals), dense)
+    assert _info(path, "data/W") == ((n, r), True, 4)
+    assert _info(path, "data/H/values") == ((len(vals),), True, 4)
+    assert _info(path, "data/H/row_indices") == ((r + 1,), False, 8)      # int64, as the sparsify script writes
+    assert _info(path, "data/H/column_indices") == ((len(vals),), False, 4)
+    assert _info(path, "data/reduce_kept_indices") == ((m,), False, 4)
+    W2 = np.empty_like(W)
+    rp2 = np.empty(r + 1, np.int64)
+    c2 = np.empty(len(vals), np.int32)
+    v2 = np.empty(len(vals), np.float32)
+    k2 = np.empty(m, np.int32)
+    check(lib().dnpeff_read_sparse_decomposition_hdf5(
+        path.encode(), C.c_void_p(W2.ctypes.data), C.c_void_p(rp2.ctypes.data), C.c_void_p(c2.ctypes.data),
+        C.c_void_p(v2.ctypes.data), C.c_void_p(k2.ctypes.data)))
+    assert np.array_equal(W2, W) and np.array_equal(rp2, rowptr) and np.array_equal(c2, cols)
+    assert np.array_equal(v2, vals) and np.array_equal(k2, kept)
+    # a dense decomposition file is not a sparse one, and the other way round
+    dpath = str(tmp_path / "dense.h5")
+    check(lib().dnpeff_save_decomposition_hdf5(dpath.encode(), C.c_void_p(W.ctypes.data), C.c_void_p(H.ctypes.data),
+                                               C.c_void_p(kept.ctypes.data), n, r, m, dense))
+    assert lib().dnpeff_sparse_decomposition_hdf5_info(dpath.encode(), None, None, None, None, None) != 0
+    assert lib().dnpeff_decomposition_hdf5_info(path.encode(), None, None, None, None) != 0

@@ -175,3 +175,34 @@ def test_oracle_matches_reference_engine(path):
     # carries ~1e-4 of cancellation noise; compare at 1e-3.
     assert abs(ls[-1] - float(g["loss"])) < 1e-3 * ls[-1]
     assert abs(O.loss(v, c, rp, mk, g["W0"], g["H0"]) - float(g["loss0"])) < 1e-3 * float(g["loss0"])
+
+
+def test_retain_columns_known_answer_and_properties():
+    """RetainColumns_InPlace (src/cuda/host/sparse_matrix.h:141-170) worked by hand:
+    new index = position in the list, other entries dropped, row order kept."""
+    #      col: 0    1    2    3    4
+    # row 0:   1.        2.        3.
+    # row 1:        4.
+    # row 2:   5.   6.        7.
+    vals = np.array([1, 2, 3, 4, 5, 6, 7], np.float32)
+    col = np.array([0, 2, 4, 1, 0, 1, 3], np.int32)
+    rp = np.array([0, 3, 4, 7], np.int64)
+    v, c, p = O.retain_columns(vals, col, rp, 5, [4, 0, 3])
+    assert v.tolist() == [1, 3, 5, 7] and c.tolist() == [1, 0, 1, 2] and p.tolist() == [0, 2, 2, 4]
+    # a repeated id keeps its last position; an id with no entries is simply an empty column
+    v, c, p = O.retain_columns(vals, col, rp, 5, [1, 2, 1])
+    assert v.tolist() == [2, 4, 6] and c.tolist() == [1, 2, 2] and p.tolist() == [0, 1, 2, 3]
+    # retaining the pruning's own kept list reproduces the pruning
+    vals2, idx2, norms2 = make_problem(40, 500, 30, seed=4)
+    pv, pc, prp, n2o = oracle_preprocess(vals2, idx2, norms2, 500, 2)
+    rowptr = np.arange(41, dtype=np.int64) * 30
+    nv = O.normalize_rows(vals2.ravel(), rowptr, norms2)
+    rv, rc, rrp = O.retain_columns(nv, idx2.ravel(), rowptr, 500, n2o)
+    assert np.array_equal(rv, pv) and np.array_equal(rc, pc) and np.array_equal(rrp, prp)
+
+
+def test_dense_to_csr_thresholding():
+    A = np.array([[0.5, 0.0, 0.2], [0.0, 0.0, 0.0], [0.1, 0.3, 0.3]], np.float32)
+    v, rp, c = O.dense_to_csr(A, 0.2)
+    assert v.tolist() == pytest.approx([0.5, 0.2, 0.3, 0.3]) and rp.tolist() == [0, 2, 2, 4] and c.tolist() == [0, 2, 1, 2]
+    assert rp.dtype == np.int64 and c.dtype == np.int32
