@@ -1253,6 +1253,12 @@ int dnpeff_comm_init(dnpeff_engine* e, const void* id128, int comm_rank, int com
     e->comm_rank = comm_rank;
     e->comm_size = comm_size;
     e->a_sq_global = -1.0;
+    // NCCL connects its channels on the first collective (hundreds of ms): do that
+    // here, as part of joining, not inside the first iteration
+    DevBuf<float> one;
+    DN_TRY(one.alloc_zero(32, e->st));
+    DN_NCCL(nccl_api().AllReduce(one.p, one.p, 32, ncclFloat, ncclSum, e->comm, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
     return DNPEFF_OK;
 }
 
