@@ -102,7 +102,7 @@ struct dnpeff_engine {
 
     int64_t n = 0, m_full = 0, m_kept = 0, c0 = 0, ms = 0, nnz = 0;
     ShardMap map = {0, 0, 1, 0, 0};
-    bool loaded = false, have_factors = false, csc_ready = false;
+    bool loaded = false, have_factors = false, csc_ready = false, csc_hot_ready = false;
 
     float* a_vals = nullptr;
     int32_t* a_col = nullptr;
@@ -167,7 +167,11 @@ int check_kernel_status(dnpeff_engine* e);
 
 constexpr int kRedBlocks = 4 * kNumSMs;
 constexpr int kMaxHotTiles = 1024;            // tiles of popular columns per row walk
-constexpr int64_t kTailBlockBytes = 24 << 20;  // slice of H gathered per tail launch (L2-resident)
+// Slice of H gathered per tail launch.  It has to stay L2-resident while all rows
+// sweep it; every further launch costs about 11 us.  Measured on the headline
+// workload (A*H^T product, ms): 12 MB 12.8, 24 MB 12.0, 32 MB 11.7, 48 MB 11.4,
+// 64 MB 11.7, 96 MB 14.2.
+constexpr int64_t kTailBlockBytes = 48 << 20;
 constexpr int kMaxTailBlocks = 512;
 
 struct DeviceGuard {
@@ -219,6 +223,26 @@ bool tensor_cores_enabled() {
     return v == 1;
 }
 
+// DNPEFF_TRACE=1 prints the wall time of the loader's phases to stderr (each
+// phase is closed with a stream synchronisation, so the trace slows the load).
+struct PhaseTrace {
+    cudaStream_t st;
+    bool on;
+    std::chrono::high_resolution_clock::time_point t;
+    explicit PhaseTrace(cudaStream_t s) : st(s) {
+        const char* v = getenv("DNPEFF_TRACE");
+        on = v && v[0] == '1';
+        if (on) t = std::chrono::high_resolution_clock::now();
+    }
+    void mark(const char* what) {
+        if (!on) return;
+        cudaStreamSynchronize(st);
+        auto n = std::chrono::high_resolution_clock::now();
+        fprintf(stderr, "[dnpeff] %-28s %8.2f ms\n", what, std::chrono::duration<double, std::milli>(n - t).count());
+        t = n;
+    }
+};
+
 // Popular columns hold at least ceil(n / div) entries.  With the dense tensor-core
 // block a column pays off from a few percent of density on; the sparse tiled
 // kernel needs longer columns.  DNPEFF_HOT_DIV overrides (experiments).
@@ -265,7 +289,7 @@ void free_matrix(dnpeff_engine* e) {
     dev_free(e->plan_csc.long_list);
     e->plan_csr = SpmmPlan();
     e->plan_csc = SpmmPlan();
-    e->loaded = e->have_factors = e->csc_ready = false;
+    e->loaded = e->have_factors = e->csc_ready = e->csc_hot_ready = false;
     e->a_sq_global = -1.0;
 }
 
@@ -316,6 +340,8 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DevBuf<int> err;
     DN_TRY(err.alloc_zero(1, st));
     int herr = 0;
+    PhaseTrace trace(st);
+    trace.mark("upload / inputs ready");
 
     // 1. explicit entries per original column
     DevBuf<int32_t> counts, flags, og_to_new;
@@ -330,6 +356,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_TRY(read_err_flag(err.p, st, &herr));
     if (herr) return data_error(herr);
 
+    trace.mark("count columns");
     // 2. keep mask -> ascending renumbering, or the caller's list of kept columns
     DN_TRY(og_to_new.alloc((size_t)m_full + 1));
     int64_t m_kept = 0;
@@ -366,6 +393,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         }
     }
 
+    trace.mark("pruning maps");
     // 3. this engine's range of kept columns
     int64_t c0 = 0, ms = 0;
     ShardMap map;
@@ -396,6 +424,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_TRY(read_err_flag(err.p, st, &herr));
     if (herr) return data_error(herr);
 
+    trace.mark("row counts + scan");
     // 5. order-preserving extraction with the row normalisation applied
     DN_CUDA(cudaMalloc((void**)&e->a_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
     DN_CUDA(cudaMalloc((void**)&e->a_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
@@ -408,6 +437,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         DN_COUNT_LAUNCH(1);
     }
 
+    trace.mark("extract shard");
     // 6. internal column order: popular columns first (they get the tiled,
     //    shared-memory kernels), then the rest; both parts in local-id order
     DevBuf<int32_t> cnt_s, hot_flags, cnt_p;
@@ -479,11 +509,15 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_COUNT_LAUNCH(1);
     DN_TRY(scan_exclusive<int32_t>(cnt_p.p, e->c_colptr, ms + 1, st));
 
+    trace.mark("popular columns, permutation");
     // 6b. rows of A partitioned into buckets: hot tiles, then tail column blocks
     //     narrow enough for their slice of H to stay in L2 while it is gathered
     {
         int64_t tail_cols = ms - n_hot;
-        int64_t block = std::max<int64_t>(4096, ((int64_t)kTailBlockBytes / (4 * (int64_t)r)) / 32 * 32);
+        int64_t tail_bytes = kTailBlockBytes;
+        if (const char* tb = getenv("DNPEFF_TAIL_MB"))  // experiments: size of a tail block's slice of H
+            if (atoi(tb) >= 1) tail_bytes = (int64_t)atoi(tb) << 20;
+        int64_t block = std::max<int64_t>(4096, (tail_bytes / (4 * (int64_t)r)) / 32 * 32);
         int64_t nb = ceil_div(std::max<int64_t>(tail_cols, 1), block);
         if (nb > kMaxTailBlocks) {
             block = ceil_div(ceil_div(tail_cols, kMaxTailBlocks), 32) * 32;
@@ -512,6 +546,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             DN_LAUNCH_CHECK();
             DN_COUNT_LAUNCH(1);
         }
+        trace.mark("bucket rows");
         if (dense) {
             e->plan_x1 = block_tc_plan(n, n_hot, r);
             e->plan_x2 = block_tc_plan(n_hot, n, r);
@@ -530,6 +565,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             DN_LAUNCH_CHECK();
             DN_COUNT_LAUNCH(1);
         }
+        trace.mark("dense popular block");
         // stored entries per tail block (decides warp-per-row or block-per-row launches)
         std::vector<int64_t> colptr_h;
         e->tail_nnz.assign((size_t)nb, 0);
@@ -543,6 +579,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         }
     }
 
+    trace.mark("tail block sizes");
     // 7. |A|^2 and sum(A) of the shard
     k_sum_sumsq<<<kRedBlocks, 256, 0, st>>>(e->a_vals, nnz, e->red_partial);
     DN_LAUNCH_CHECK();
@@ -569,45 +606,90 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_TRY(spmm_make_plan(e->a_rowptr, 0, n, &e->plan_csr, st));
     DN_TRY(spmm_make_plan(e->c_colptr, e->n_hot, ms - e->n_hot, &e->plan_csc, st));
     e->loaded = true;
+    trace.mark("norms, factor buffers, plans");
     return DNPEFF_OK;
 }
 
-// Stable CSC fill in waves of 64 rows (see kernels_prep.cuh).
-int build_csc(dnpeff_engine* e) {
-    if (e->csc_ready) return DNPEFF_OK;
+// Stable CSC fill, group of rows by group of rows (see kernels_prep.cuh).  `mode`:
+// 0 every entry, 1 only the entries outside the popular columns, 2 only those
+// inside.  The column offsets cover all entries in every mode.
+int fill_csc(dnpeff_engine* e, int mode) {
     cudaStream_t st = e->st;
-    DN_CUDA(cudaMalloc((void**)&e->c_vals, sizeof(float) * (size_t)std::max<int64_t>(e->nnz, 1)));
-    DN_CUDA(cudaMalloc((void**)&e->c_row, sizeof(int32_t) * (size_t)std::max<int64_t>(e->nnz, 1)));
-    if (e->nnz > 0) {
-        DevBuf<unsigned long long> mask, maxlen;
-        DevBuf<int32_t> cursor;
-        DevBuf<int> err;
-        DN_TRY(mask.alloc_zero((size_t)e->ms, st));
-        DN_TRY(cursor.alloc_zero((size_t)e->ms, st));
-        DN_TRY(maxlen.alloc_zero(1, st));
-        DN_TRY(err.alloc_zero(1, st));
-        k_max_rowlen<<<(unsigned)ceil_div(e->n, 256), 256, 0, st>>>(e->a_rowptr, e->n, maxlen.p);
+    if (e->nnz <= 0) return DNPEFF_OK;
+    RowPart part = {e->tail_off, e->n_tail_blocks + 1, mode};
+    DevBuf<unsigned long long> mask, maxlen;
+    DevBuf<int32_t> cnt;
+    DevBuf<int> err;
+    // rows per group: 64 * words, words doubled while the per-group counts would
+    // take more than 2 GB
+    int words = 8;
+    auto groups_of = [&](int w) { return ceil_div(e->n, (int64_t)64 * w); };
+    while (words < 32 && groups_of(words) * e->ms * 4 > ((int64_t)2 << 30)) words *= 2;
+    const int rows_per_group = 64 * words;
+    const int n_groups = (int)groups_of(words);
+    PhaseTrace trace(st);
+    DN_TRY(mask.alloc_zero((size_t)e->ms * words, st));
+    DN_TRY(cnt.alloc_zero((size_t)n_groups * (size_t)e->ms, st));
+    DN_TRY(maxlen.alloc_zero(1, st));
+    DN_TRY(err.alloc_zero(1, st));
+    trace.mark("  csc: scratch");
+    k_max_rowlen<<<(unsigned)ceil_div(e->n, 256), 256, 0, st>>>(e->a_rowptr, e->n, maxlen.p);
+    DN_LAUNCH_CHECK();
+    DN_COUNT_LAUNCH(1);
+    unsigned long long hmax = 0;
+    DN_CUDA(cudaMemcpyAsync(&hmax, maxlen.p, sizeof(hmax), cudaMemcpyDeviceToHost, st));
+    DN_CUDA(cudaStreamSynchronize(st));
+    if (hmax > 0) {
+        const unsigned gx = (unsigned)ceil_div((int64_t)hmax, 256);
+        for (int64_t base = 0; base < e->n; base += 32768) {  // grid.y is limited to 65535
+            dim3 cgrid(std::min(gx, 64u), (unsigned)std::min<int64_t>(32768, e->n - base));
+            k_csc_count<<<cgrid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, part, rows_per_group, e->ms, cnt.p);
+            DN_COUNT_LAUNCH(1);
+        }
+        DN_LAUNCH_CHECK();
+        trace.mark("  csc: count");
+        k_csc_group_bases<<<(unsigned)ceil_div(e->ms, 256), 256, 0, st>>>(cnt.p, n_groups, e->ms);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
-        unsigned long long hmax = 0;
-        DN_CUDA(cudaMemcpyAsync(&hmax, maxlen.p, sizeof(hmax), cudaMemcpyDeviceToHost, st));
-        DN_CUDA(cudaStreamSynchronize(st));
-        if (hmax > 0) {
-            dim3 grid((unsigned)ceil_div((int64_t)hmax, 256), 64);
-            for (int64_t base = 0; base < e->n; base += 64) {
-                k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, mask.p, err.p);
-                k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, base, e->n, mask.p,
-                                                  e->c_colptr, cursor.p, e->c_vals, e->c_row);
-                k_csc_advance<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, mask.p, cursor.p);
-                DN_COUNT_LAUNCH(3);
-            }
-            DN_LAUNCH_CHECK();
+        for (int g = 0; g < n_groups; g++) {
+            const int64_t base = (int64_t)g * rows_per_group;
+            dim3 grid(gx, (unsigned)std::min<int64_t>(rows_per_group, e->n - base));
+            k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, part, words, mask.p, err.p);
+            k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, base, e->n, part, words, mask.p,
+                                              e->c_colptr, cnt.p + (int64_t)g * e->ms, e->c_vals, e->c_row);
+            DN_COUNT_LAUNCH(2);
+            if (g + 1 < n_groups)
+                DN_CUDA(cudaMemsetAsync(mask.p, 0, sizeof(unsigned long long) * (size_t)e->ms * words, st));
         }
-        int herr = 0;
-        DN_TRY(read_err_flag(err.p, st, &herr));
-        if (herr) return data_error(herr);
+        DN_LAUNCH_CHECK();
+        trace.mark("  csc: mark + place");
     }
-    e->csc_ready = true;
+    int herr = 0;
+    DN_TRY(read_err_flag(err.p, st, &herr));
+    if (herr) return data_error(herr);
+    return DNPEFF_OK;
+}
+
+// The CSC the H update needs.  With the popular block kept dense the popular
+// columns are never read from the CSC, so they are filled only on demand
+// (`full`: the export call).
+int build_csc(dnpeff_engine* e, bool full = false) {
+    PhaseTrace trace(e->st);
+    if (!e->csc_ready) {
+        trace.mark("(before CSC build)");
+        DN_CUDA(cudaMalloc((void**)&e->c_vals, sizeof(float) * (size_t)std::max<int64_t>(e->nnz, 1)));
+        DN_CUDA(cudaMalloc((void**)&e->c_row, sizeof(int32_t) * (size_t)std::max<int64_t>(e->nnz, 1)));
+        trace.mark("  csc: arrays allocated");
+        const bool tail_only = e->x2 != nullptr && !full;
+        DN_TRY(fill_csc(e, tail_only ? 1 : 0));
+        e->csc_ready = true;
+        e->csc_hot_ready = !tail_only;
+        trace.mark("CSC build");
+    }
+    if (full && !e->csc_hot_ready) {
+        DN_TRY(fill_csc(e, 2));
+        e->csc_hot_ready = true;
+    }
     return DNPEFF_OK;
 }
 
@@ -1085,7 +1167,7 @@ int dnpeff_export_shard_csr(dnpeff_engine* e, int64_t* rowptr, int32_t* colind, 
 int dnpeff_export_shard_csc(dnpeff_engine* e, int64_t* colptr, int32_t* rowind, float* vals) {
     DN_TRY(check_ready(e, false));
     DeviceGuard g(e->device);
-    DN_TRY(build_csc(e));
+    DN_TRY(build_csc(e, true));
     // The device CSC is in the engine's internal column order; hand it out in
     // local column order (a test/debug path: reordered on the host).
     std::vector<int64_t> cp((size_t)e->ms + 1);

@@ -257,54 +257,86 @@ __global__ void k_gather_counts(const int32_t* __restrict__ counts,
 }
 
 // ---- CSC build --------------------------------------------------------------
-// A stable transpose (rows ascending inside every column) without a sort: rows
-// are taken in waves of 64; inside a wave every column collects a 64-bit mask
-// of the wave rows that hold it (atomicOr: order-independent), an entry's slot
-// is colptr + entries placed by earlier waves + popcount of the lower mask
-// bits.  Deterministic, integer atomics only.  grid = (ceil(maxlen/256), 64).
+// A stable transpose (rows ascending inside every column) without a sort.  Rows
+// are cut into groups of 64*words rows.  Pass 1 counts every column's entries per
+// group (integer atomics), pass 2 turns the counts into each group's first slot
+// inside the column, then group by group every column collects a bit mask of the
+// group rows that hold it (atomicOr: order-independent) and an entry's slot is
+// colptr + group base + popcount of the lower mask bits.  Deterministic, integer
+// atomics only.  cnt is [n_groups][n_cols], mask is [n_cols][words].
+// Which part of every (bucketed) row a CSC pass covers: all of it, only the entries
+// after the popular part, or only the popular part (hot_len[row * stride] entries
+// at the row's start).
+struct RowPart {
+    const uint32_t* hot_len;
+    int stride;
+    int mode;  // 0 all, 1 after the popular part, 2 the popular part
+    __device__ void range(const int64_t* rowptr, int64_t row, int64_t& b, int64_t& e) const {
+        b = rowptr[row];
+        e = rowptr[row + 1];
+        if (mode == 1) b += hot_len[row * stride];
+        else if (mode == 2) e = b + hot_len[row * stride];
+    }
+};
+
+__global__ void k_csc_count(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
+                            int64_t row_base, int64_t n_rows, RowPart part, int rows_per_group, int64_t n_cols,
+                            int32_t* __restrict__ cnt) {
+    const int64_t row = row_base + blockIdx.y;
+    if (row >= n_rows) return;
+    int64_t beg, end;
+    part.range(rowptr, row, beg, end);
+    int32_t* c = cnt + (row / rows_per_group) * n_cols;  // rows are numbered from the matrix's first row
+    for (int64_t p = beg + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < end; p += (int64_t)gridDim.x * blockDim.x)
+        atomicAdd(c + colind[p], 1);
+}
+
+// cnt[g][j] <- sum of cnt[g'][j] over g' < g.
+__global__ void k_csc_group_bases(int32_t* __restrict__ cnt, int n_groups, int64_t n_cols) {
+    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n_cols) return;
+    int32_t run = 0;
+    for (int g = 0; g < n_groups; g++) {
+        int32_t t = cnt[(int64_t)g * n_cols + j];
+        cnt[(int64_t)g * n_cols + j] = run;
+        run += t;
+    }
+}
+
+// grid = (ceil(maxlen/256), rows of the group)
 __global__ void k_csc_mark(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                           int64_t row_base, int64_t n_rows,
+                           int64_t row_base, int64_t n_rows, RowPart part, int words,
                            unsigned long long* __restrict__ mask, int* __restrict__ err) {
     int64_t row = row_base + blockIdx.y;
     if (row >= n_rows) return;
-    int64_t p = rowptr[row] + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= rowptr[row + 1]) return;
-    unsigned long long bit = 1ull << blockIdx.y;
-    unsigned long long old = atomicOr(mask + colind[p], bit);
+    int64_t beg, end;
+    part.range(rowptr, row, beg, end);
+    int64_t p = beg + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= end) return;
+    unsigned long long bit = 1ull << (blockIdx.y & 63);
+    unsigned long long old = atomicOr(mask + (int64_t)colind[p] * words + (blockIdx.y >> 6), bit);
     if (old & bit) atomicOr(err, kErrDuplicate);
 }
 
 __global__ void k_csc_place(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                            const float* __restrict__ vals, int64_t row_base, int64_t n_rows,
-                            const unsigned long long* __restrict__ mask,
-                            const int64_t* __restrict__ colptr, const int32_t* __restrict__ cursor,
+                            const float* __restrict__ vals, int64_t row_base, int64_t n_rows, RowPart part,
+                            int words, const unsigned long long* __restrict__ mask,
+                            const int64_t* __restrict__ colptr, const int32_t* __restrict__ group_base,
                             float* __restrict__ cvals, int32_t* __restrict__ crow) {
     int64_t row = row_base + blockIdx.y;
     if (row >= n_rows) return;
-    int64_t p = rowptr[row] + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= rowptr[row + 1]) return;
+    int64_t beg, end;
+    part.range(rowptr, row, beg, end);
+    int64_t p = beg + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= end) return;
     int32_t j = colind[p];
-    unsigned long long bit = 1ull << blockIdx.y;
-    int64_t q = colptr[j] + cursor[j] + __popcll(mask[j] & (bit - 1ull));
+    const unsigned long long* m = mask + (int64_t)j * words;
+    const int wi = blockIdx.y >> 6;
+    int rank = __popcll(m[wi] & ((1ull << (blockIdx.y & 63)) - 1ull));
+    for (int w = 0; w < wi; w++) rank += __popcll(m[w]);
+    int64_t q = colptr[j] + group_base[j] + rank;
     cvals[q] = vals[p];
     crow[q] = (int32_t)row;
-}
-
-__global__ void k_csc_advance(const int64_t* __restrict__ rowptr,
-                              const int32_t* __restrict__ colind, int64_t row_base, int64_t n_rows,
-                              unsigned long long* __restrict__ mask, int32_t* __restrict__ cursor) {
-    int64_t row = row_base + blockIdx.y;
-    if (row >= n_rows) return;
-    int64_t p = rowptr[row] + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= rowptr[row + 1]) return;
-    int32_t j = colind[p];
-    unsigned long long mk = mask[j];
-    // Only the entry of the highest wave row of this column advances it; any
-    // other entry sees either the full mask or the cleared one, never "highest".
-    if ((mk >> blockIdx.y) == 1ull) {
-        cursor[j] += __popcll(mk);
-        mask[j] = 0ull;
-    }
 }
 
 // ---- internal column order and row buckets -----------------------------------

@@ -302,6 +302,10 @@ def test_popular_block_is_dense_and_matches_oracle(torch_cuda):
         assert rel_fro(H1, Ho1) < 2e-6
         # element-wise too: a popular column must not differ from a tail column in accuracy
         assert np.max(np.abs(H1 - Ho1) / (np.abs(Ho1) + 1e-30)) < 1e-4
+        # the H update built only the tail part of the CSC; the export completes it
+        cv, cr, cp = O.csr_to_csc(v, c, rp, mk)
+        hv, hr, hp = eng.export_shard_csc()
+        assert np.array_equal(hp, cp) and np.array_equal(hr, cr) and np.array_equal(hv, cv)
     # a rank outside the tensor-core set keeps the sparse tiled kernel
     with _engine(MuNmfParams(rank=48, eps=eps, seed=2, init_scale=scale)) as eng:
         eng.set_csr(n, m, vals, idx, None, k, norms, 1)
