@@ -254,13 +254,13 @@ int hot_divisor(bool dense) {
 
 // G = X^T X: tcgen05 kernel where the rank allows, CUDA-core kernel otherwise.
 int gram_any(const float* X, int64_t rows, int r, float* G, float* scratch, int* err, cudaStream_t st) {
-    if (tensor_cores_enabled() && gram_tc_ok(r)) return gram_tc_launch(X, rows, r, G, scratch, err, st);
+    if (tensor_cores_enabled() && gram_tc_ok(r)) return gram_blk_launch(X, rows, r, G, scratch, err, st);
     return gram_launch(X, rows, r, G, scratch, st);
 }
 
 size_t gram_any_scratch(int64_t rows, int r) {
     size_t a = gram_plan(rows, r).scratch_floats;
-    size_t b = gram_tc_ok(r) ? gram_tc_plan(rows, r).scratch_floats : 0;
+    size_t b = gram_tc_ok(r) ? gram_blk_plan(rows).scratch_floats : 0;
     return a > b ? a : b;
 }
 
