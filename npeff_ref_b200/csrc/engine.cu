@@ -615,9 +615,13 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
 // inside.  The column offsets cover all entries in every mode.
 int fill_csc(dnpeff_engine* e, int mode) {
     cudaStream_t st = e->st;
-    if (e->nnz <= 0) return DNPEFF_OK;
-    RowPart part = {e->tail_off, e->n_tail_blocks + 1, mode};
-    DevBuf<unsigned long long> mask, maxlen;
+    if (e->nnz <= 0 || e->n <= 0) return DNPEFF_OK;
+    // segments of a bucketed row: 0 = the popular part, s >= 1 = tail block s-1
+    const int n_seg_all = e->n_tail_blocks + 1;
+    RowSegments segs = {e->tail_off, e->n_tail_blocks + 1, mode == 1 ? 1 : 0};
+    const int n_seg = mode == 0 ? n_seg_all : (mode == 1 ? n_seg_all - 1 : 1);
+    if (n_seg <= 0) return DNPEFF_OK;
+    DevBuf<unsigned long long> mask;
     DevBuf<int32_t> cnt;
     DevBuf<int> err;
     // rows per group: 64 * words, words doubled while the per-group counts would
@@ -630,40 +634,30 @@ int fill_csc(dnpeff_engine* e, int mode) {
     PhaseTrace trace(st);
     DN_TRY(mask.alloc_zero((size_t)e->ms * words, st));
     DN_TRY(cnt.alloc_zero((size_t)n_groups * (size_t)e->ms, st));
-    DN_TRY(maxlen.alloc_zero(1, st));
     DN_TRY(err.alloc_zero(1, st));
     trace.mark("  csc: scratch");
-    k_max_rowlen<<<(unsigned)ceil_div(e->n, 256), 256, 0, st>>>(e->a_rowptr, e->n, maxlen.p);
-    DN_LAUNCH_CHECK();
-    DN_COUNT_LAUNCH(1);
-    unsigned long long hmax = 0;
-    DN_CUDA(cudaMemcpyAsync(&hmax, maxlen.p, sizeof(hmax), cudaMemcpyDeviceToHost, st));
-    DN_CUDA(cudaStreamSynchronize(st));
-    if (hmax > 0) {
-        const unsigned gx = (unsigned)ceil_div((int64_t)hmax, 256);
-        for (int64_t base = 0; base < e->n; base += 32768) {  // grid.y is limited to 65535
-            dim3 cgrid(std::min(gx, 64u), (unsigned)std::min<int64_t>(32768, e->n - base));
-            k_csc_count<<<cgrid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, part, rows_per_group, e->ms, cnt.p);
-            DN_COUNT_LAUNCH(1);
-        }
+    {
+        dim3 grid((unsigned)ceil_div(e->n, 8), (unsigned)n_seg);
+        k_csc_count<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->n, segs, rows_per_group, e->ms, cnt.p);
         DN_LAUNCH_CHECK();
-        trace.mark("  csc: count");
         k_csc_group_bases<<<(unsigned)ceil_div(e->ms, 256), 256, 0, st>>>(cnt.p, n_groups, e->ms);
         DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(1);
-        for (int g = 0; g < n_groups; g++) {
-            const int64_t base = (int64_t)g * rows_per_group;
-            dim3 grid(gx, (unsigned)std::min<int64_t>(rows_per_group, e->n - base));
-            k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, e->n, part, words, mask.p, err.p);
-            k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, base, e->n, part, words, mask.p,
-                                              e->c_colptr, cnt.p + (int64_t)g * e->ms, e->c_vals, e->c_row);
-            DN_COUNT_LAUNCH(2);
-            if (g + 1 < n_groups)
-                DN_CUDA(cudaMemsetAsync(mask.p, 0, sizeof(unsigned long long) * (size_t)e->ms * words, st));
-        }
-        DN_LAUNCH_CHECK();
-        trace.mark("  csc: mark + place");
+        DN_COUNT_LAUNCH(2);
     }
+    trace.mark("  csc: count");
+    for (int g = 0; g < n_groups; g++) {
+        const int64_t base = (int64_t)g * rows_per_group;
+        const int rows_in_group = (int)std::min<int64_t>(rows_per_group, e->n - base);
+        dim3 grid((unsigned)ceil_div(rows_in_group, 8), (unsigned)n_seg);
+        k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, rows_in_group, segs, words, mask.p, err.p);
+        k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, base, rows_in_group, segs, words, mask.p,
+                                          e->c_colptr, cnt.p + (int64_t)g * e->ms, e->c_vals, e->c_row);
+        DN_COUNT_LAUNCH(2);
+        if (g + 1 < n_groups)
+            DN_CUDA(cudaMemsetAsync(mask.p, 0, sizeof(unsigned long long) * (size_t)e->ms * words, st));
+    }
+    DN_LAUNCH_CHECK();
+    trace.mark("  csc: mark + place");
     int herr = 0;
     DN_TRY(read_err_flag(err.p, st, &herr));
     if (herr) return data_error(herr);

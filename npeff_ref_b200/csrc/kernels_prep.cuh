@@ -264,31 +264,33 @@ __global__ void k_gather_counts(const int32_t* __restrict__ counts,
 // group rows that hold it (atomicOr: order-independent) and an entry's slot is
 // colptr + group base + popcount of the lower mask bits.  Deterministic, integer
 // atomics only.  cnt is [n_groups][n_cols], mask is [n_cols][words].
-// Which part of every (bucketed) row a CSC pass covers: all of it, only the entries
-// after the popular part, or only the popular part (hot_len[row * stride] entries
-// at the row's start).
-struct RowPart {
-    const uint32_t* hot_len;
-    int stride;
-    int mode;  // 0 all, 1 after the popular part, 2 the popular part
-    __device__ void range(const int64_t* rowptr, int64_t row, int64_t& b, int64_t& e) const {
-        b = rowptr[row];
-        e = rowptr[row + 1];
-        if (mode == 1) b += hot_len[row * stride];
-        else if (mode == 2) e = b + hot_len[row * stride];
+// The bucketed rows are walked segment by segment: segment 0 is a row's popular
+// part, segment s >= 1 its entries in tail column block s-1 (tail_off[row][s-1] ..
+// tail_off[row][s]).  One warp per (row, segment), segments along grid.y so that
+// the passes run segment after segment: the masks, counts and CSC slots a segment
+// touches belong to one block of columns and stay in L2.
+struct RowSegments {
+    const uint32_t* tail_off;  // [rows][n_tail + 1]
+    int stride;                // n_tail + 1
+    int first;                 // first segment the pass covers (grid.y = 0)
+    __device__ void range(const int64_t* rowptr, int64_t row, int seg, int64_t& b, int64_t& e) const {
+        const int64_t r0 = rowptr[row];
+        const uint32_t* t = tail_off + row * stride;
+        b = r0 + (seg == 0 ? 0u : t[seg - 1]);
+        e = r0 + t[seg];
     }
 };
 
+// grid = (ceil(rows / 8), segments), 256 threads
 __global__ void k_csc_count(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                            int64_t row_base, int64_t n_rows, RowPart part, int rows_per_group, int64_t n_cols,
+                            int64_t n_rows, RowSegments segs, int rows_per_group, int64_t n_cols,
                             int32_t* __restrict__ cnt) {
-    const int64_t row = row_base + blockIdx.y;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= n_rows) return;
     int64_t beg, end;
-    part.range(rowptr, row, beg, end);
-    int32_t* c = cnt + (row / rows_per_group) * n_cols;  // rows are numbered from the matrix's first row
-    for (int64_t p = beg + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < end; p += (int64_t)gridDim.x * blockDim.x)
-        atomicAdd(c + colind[p], 1);
+    segs.range(rowptr, row, segs.first + blockIdx.y, beg, end);
+    int32_t* c = cnt + (row / rows_per_group) * n_cols;
+    for (int64_t p = beg + (threadIdx.x & 31); p < end; p += 32) atomicAdd(c + colind[p], 1);
 }
 
 // cnt[g][j] <- sum of cnt[g'][j] over g' < g.
@@ -303,40 +305,43 @@ __global__ void k_csc_group_bases(int32_t* __restrict__ cnt, int n_groups, int64
     }
 }
 
-// grid = (ceil(maxlen/256), rows of the group)
+// grid = (ceil(rows of the group / 8), segments), 256 threads
 __global__ void k_csc_mark(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                           int64_t row_base, int64_t n_rows, RowPart part, int words,
+                           int64_t row_base, int rows_in_group, RowSegments segs, int words,
                            unsigned long long* __restrict__ mask, int* __restrict__ err) {
-    int64_t row = row_base + blockIdx.y;
-    if (row >= n_rows) return;
+    const int rig = blockIdx.x * 8 + (threadIdx.x >> 5);  // row inside the group
+    if (rig >= rows_in_group) return;
     int64_t beg, end;
-    part.range(rowptr, row, beg, end);
-    int64_t p = beg + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= end) return;
-    unsigned long long bit = 1ull << (blockIdx.y & 63);
-    unsigned long long old = atomicOr(mask + (int64_t)colind[p] * words + (blockIdx.y >> 6), bit);
-    if (old & bit) atomicOr(err, kErrDuplicate);
+    segs.range(rowptr, row_base + rig, segs.first + blockIdx.y, beg, end);
+    const unsigned long long bit = 1ull << (rig & 63);
+    const int wi = rig >> 6;
+    for (int64_t p = beg + (threadIdx.x & 31); p < end; p += 32) {
+        unsigned long long old = atomicOr(mask + (int64_t)colind[p] * words + wi, bit);
+        if (old & bit) atomicOr(err, kErrDuplicate);
+    }
 }
 
 __global__ void k_csc_place(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                            const float* __restrict__ vals, int64_t row_base, int64_t n_rows, RowPart part,
-                            int words, const unsigned long long* __restrict__ mask,
+                            const float* __restrict__ vals, int64_t row_base, int rows_in_group,
+                            RowSegments segs, int words, const unsigned long long* __restrict__ mask,
                             const int64_t* __restrict__ colptr, const int32_t* __restrict__ group_base,
                             float* __restrict__ cvals, int32_t* __restrict__ crow) {
-    int64_t row = row_base + blockIdx.y;
-    if (row >= n_rows) return;
+    const int rig = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (rig >= rows_in_group) return;
+    const int64_t row = row_base + rig;
     int64_t beg, end;
-    part.range(rowptr, row, beg, end);
-    int64_t p = beg + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= end) return;
-    int32_t j = colind[p];
-    const unsigned long long* m = mask + (int64_t)j * words;
-    const int wi = blockIdx.y >> 6;
-    int rank = __popcll(m[wi] & ((1ull << (blockIdx.y & 63)) - 1ull));
-    for (int w = 0; w < wi; w++) rank += __popcll(m[w]);
-    int64_t q = colptr[j] + group_base[j] + rank;
-    cvals[q] = vals[p];
-    crow[q] = (int32_t)row;
+    segs.range(rowptr, row, segs.first + blockIdx.y, beg, end);
+    const unsigned long long lower = (1ull << (rig & 63)) - 1ull;
+    const int wi = rig >> 6;
+    for (int64_t p = beg + (threadIdx.x & 31); p < end; p += 32) {
+        const int32_t j = colind[p];
+        const unsigned long long* m = mask + (int64_t)j * words;
+        int rank = __popcll(m[wi] & lower);
+        for (int w = 0; w < wi; w++) rank += __popcll(m[w]);
+        const int64_t q = colptr[j] + group_base[j] + rank;
+        cvals[q] = vals[p];
+        crow[q] = (int32_t)row;
+    }
 }
 
 // ---- internal column order and row buckets -----------------------------------
