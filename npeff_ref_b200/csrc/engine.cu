@@ -317,7 +317,7 @@ void shard_range(int64_t total, int n_shards, int idx, int64_t* start, int64_t* 
 // pointer, n_retained of them) instead of the columns with >= min_count entries.
 int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const int64_t* d_rowptr,
                 const float* d_vals, const int32_t* d_col, const float* d_norms, int32_t min_count,
-                const int32_t* d_retained = nullptr, int64_t n_retained = 0) {
+                const int32_t* d_retained = nullptr, int64_t n_retained = 0, cudaEvent_t vals_ready = nullptr) {
     if (n < 0 || m_full < 0 || (d_rowptr == nullptr && k < 0))
         return fail(DNPEFF_ERR_INVALID, "negative shape");
     if (n >= INT32_MAX || m_full >= INT32_MAX)
@@ -425,6 +425,9 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     if (herr) return data_error(herr);
 
     trace.mark("row counts + scan");
+    // (the values may still be on their way from the host: everything up to here
+    // needed the column ids only)
+    if (vals_ready) DN_CUDA(cudaStreamWaitEvent(st, vals_ready, 0));
     // 5. order-preserving extraction with the row normalisation applied
     DN_CUDA(cudaMalloc((void**)&e->a_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
     DN_CUDA(cudaMalloc((void**)&e->a_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
@@ -1070,9 +1073,29 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
     DevBuf<int64_t> dr;
     DN_TRY(dv.alloc((size_t)nnz));
     DN_TRY(dc.alloc((size_t)nnz));
+    // The column ids go first, on the engine's stream; the values (and norms) follow on
+    // a second stream, so that counting, pruning and the row offsets overlap their upload.
+    cudaStream_t up = nullptr;
+    cudaEvent_t vals_ready = nullptr;
+    struct UploadGuard {
+        cudaStream_t& s;
+        cudaEvent_t& ev;
+        ~UploadGuard() {
+            if (s) { cudaStreamSynchronize(s); cudaStreamDestroy(s); }
+            if (ev) cudaEventDestroy(ev);
+        }
+    } upload_guard{up, vals_ready};
     if (nnz > 0) {
-        DN_CUDA(cudaMemcpyAsync(dv.p, vals, sizeof(float) * (size_t)nnz, cudaMemcpyHostToDevice, e->st));
         DN_CUDA(cudaMemcpyAsync(dc.p, colind, sizeof(int32_t) * (size_t)nnz, cudaMemcpyHostToDevice, e->st));
+        DN_CUDA(cudaStreamCreateWithFlags(&up, cudaStreamNonBlocking));
+        DN_CUDA(cudaEventCreateWithFlags(&vals_ready, cudaEventDisableTiming));
+        // the copy engine takes the transfers in issue order: ids first
+        cudaEvent_t ids_issued = nullptr;
+        DN_CUDA(cudaEventCreateWithFlags(&ids_issued, cudaEventDisableTiming));
+        DN_CUDA(cudaEventRecord(ids_issued, e->st));
+        DN_CUDA(cudaStreamWaitEvent(up, ids_issued, 0));
+        cudaEventDestroy(ids_issued);
+        DN_CUDA(cudaMemcpyAsync(dv.p, vals, sizeof(float) * (size_t)nnz, cudaMemcpyHostToDevice, up));
     }
     if (rowptr) {
         DN_TRY(dr.alloc((size_t)n_rows + 1));
@@ -1083,6 +1106,7 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
         if (n_rows > 0)
             DN_CUDA(cudaMemcpyAsync(dn.p, norms, sizeof(float) * (size_t)n_rows, cudaMemcpyHostToDevice, e->st));
     }
+    if (vals_ready) DN_CUDA(cudaEventRecord(vals_ready, up));
     DevBuf<int32_t> dret;
     if (retained) {
         DN_TRY(dret.alloc((size_t)std::max<int64_t>(n_retained, 1)));
@@ -1090,7 +1114,8 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
             DN_CUDA(cudaMemcpyAsync(dret.p, retained, sizeof(int32_t) * (size_t)n_retained, cudaMemcpyHostToDevice, e->st));
     }
     int s = load_device(e, n_rows, n_cols_full, k_per_row, rowptr ? dr.p : nullptr, dv.p, dc.p,
-                        norms ? dn.p : nullptr, min_values_per_parameter, retained ? dret.p : nullptr, n_retained);
+                        norms ? dn.p : nullptr, min_values_per_parameter, retained ? dret.p : nullptr, n_retained,
+                        vals_ready);
     if (s != DNPEFF_OK) free_matrix(e);
     cudaStreamSynchronize(e->st);
     return s;
@@ -1479,6 +1504,32 @@ int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows
     DN_TRY(op_err_word(&err));
     DN_TRY(mu_update_any(X, Num, G, rows, r, eps, scratch, err, (cudaStream_t)stream));
     return op_check_err(err, (cudaStream_t)stream);
+}
+
+int dnpeff_op_block_product(const float* X, int64_t M, int64_t K, const float* Y, int32_t r, float* C,
+                            void* stream) {
+    if (M < 0 || K < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
+    if (!block_tc_ok(r)) return fail(DNPEFF_ERR_UNSUPPORTED, "rank must be 32, 64, 96 or 128");
+    if (M == 0) return DNPEFF_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (K == 0) {
+        DN_CUDA(cudaMemsetAsync(C, 0, sizeof(float) * (size_t)(M * r), st));
+        return DNPEFF_OK;
+    }
+    BlockTcPlan p = block_tc_plan(M, K, r);
+    DevBuf<float> xb, ysplit, partial;
+    DN_TRY(xb.alloc(p.x_floats));
+    DN_TRY(ysplit.alloc(p.ysplit_floats));
+    DN_TRY(partial.alloc(p.partial_floats));
+    int* err = nullptr;
+    DN_TRY(op_err_word(&err));
+    k_block_layout<<<(unsigned)ceil_div((int64_t)(p.x_floats / 4), 256), 256, 0, st>>>(X, M, K, p.m_tiles, p.k_chunks,
+                                                                                      xb.p);
+    DN_LAUNCH_CHECK();
+    DN_TRY(block_tc_launch(xb.p, p, Y, M, K, r, C, ysplit.p, partial.p, err, st));
+    int s = op_check_err(err, st);
+    DN_CUDA(cudaStreamSynchronize(st));  // the scratch buffers are released on return
+    return s;
 }
 
 }  // extern "C"

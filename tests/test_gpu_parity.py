@@ -224,6 +224,35 @@ def test_seeded_init_bit_exact(torch_cuda):
             assert np.array_equal(eng.load_h_to_host(), H0)
 
 
+@pytest.mark.parametrize("M,K,r", [(1, 1, 32), (127, 63, 64), (128, 64, 128), (129, 65, 96), (1000, 777, 128),
+                                   (20000, 300, 32), (5000, 4100, 128), (300, 9000, 64)])
+def test_op_block_product_matches_float64(torch_cuda, M, K, r):
+    """The tensor-core kernel of the dense popular block on its own: C = X Y against a
+    float64 product, with the sparsity and value range of a popular block (a quarter
+    of X non-zero), ragged tiles and K chunks, several K splits."""
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    rng = np.random.default_rng(M * 31 + K * 7 + r)
+    X = (rng.random((M, K), dtype=np.float32) * (rng.random((M, K)) < 0.25)).astype(np.float32)
+    Y = rng.random((K, r), dtype=np.float32)
+    want = X.astype(np.float64) @ Y.astype(np.float64)
+    dX, dY = _dev(torch, X), _dev(torch, Y)
+    C_ = torch.full((M, r), float("nan"), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    check(lib().dnpeff_op_block_product(dX.data_ptr(), M, K, dY.data_ptr(), r, C_.data_ptr(), st))
+    torch.cuda.synchronize()
+    got = C_.cpu().numpy()
+    # fp32-equivalent: relative to each row's scale (sum of |x||y|), 3xTF32 leaves ~1e-6
+    scale = np.abs(X).astype(np.float64) @ np.abs(Y).astype(np.float64)
+    assert np.all(np.isfinite(got))
+    assert np.abs(got - want).max() <= 2e-6 * max(scale.max(), 1e-30)
+    # twice the same bits
+    C2 = torch.empty((M, r), device="cuda")
+    check(lib().dnpeff_op_block_product(dX.data_ptr(), M, K, dY.data_ptr(), r, C2.data_ptr(), st))
+    torch.cuda.synchronize()
+    assert np.array_equal(C2.cpu().numpy(), got)
+
+
 # ---------------------------------------------------------------------------
 CASES = [
     # n, m, k, r, iters, eps
