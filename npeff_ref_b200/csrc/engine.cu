@@ -613,54 +613,61 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     return DNPEFF_OK;
 }
 
-// Stable CSC fill, group of rows by group of rows (see kernels_prep.cuh).  `mode`:
-// 0 every entry, 1 only the entries outside the popular columns, 2 only those
-// inside.  The column offsets cover all entries in every mode.
+// CSC fill (see kernels_prep.cuh): every entry takes the next slot of its column in a
+// temporary copy, then every column is put in row order.  `mode`: 0 every entry, 1
+// only the entries outside the popular columns, 2 only those inside.  The column
+// offsets cover all entries in every mode.
 int fill_csc(dnpeff_engine* e, int mode) {
     cudaStream_t st = e->st;
-    if (e->nnz <= 0 || e->n <= 0) return DNPEFF_OK;
-    // segments of a bucketed row: 0 = the popular part, s >= 1 = tail block s-1
-    const int n_seg_all = e->n_tail_blocks + 1;
-    RowSegments segs = {e->tail_off, e->n_tail_blocks + 1, mode == 1 ? 1 : 0};
-    const int n_seg = mode == 0 ? n_seg_all : (mode == 1 ? n_seg_all - 1 : 1);
-    if (n_seg <= 0) return DNPEFF_OK;
-    DevBuf<unsigned long long> mask;
-    DevBuf<int32_t> cnt;
-    DevBuf<int> err;
-    // rows per group: 64 * words, words doubled while the per-group counts would
-    // take more than 2 GB
-    int words = 8;
-    auto groups_of = [&](int w) { return ceil_div(e->n, (int64_t)64 * w); };
-    while (words < 32 && groups_of(words) * e->ms * 4 > ((int64_t)2 << 30)) words *= 2;
-    const int rows_per_group = 64 * words;
-    const int n_groups = (int)groups_of(words);
+    if (e->nnz <= 0 || e->n <= 0 || e->ms <= 0) return DNPEFF_OK;
+    const int n_seg_all = e->n_tail_blocks + 1;  // segment 0 = popular part, s >= 1 = tail block s-1
+    const int seg_first = mode == 1 ? 1 : 0, seg_last = mode == 2 ? 1 : n_seg_all;
+    const int64_t col_first = mode == 1 ? e->n_hot : 0, col_last = mode == 2 ? e->n_hot : e->ms;
+    if (seg_first >= seg_last || col_first >= col_last) return DNPEFF_OK;
+    RowSegments segs = {e->tail_off, e->n_tail_blocks + 1};
+    const size_t bitmap_bytes = 2 * (size_t)ceil_div(e->n, 32) * sizeof(uint32_t);
     PhaseTrace trace(st);
-    DN_TRY(mask.alloc_zero((size_t)e->ms * words, st));
-    DN_TRY(cnt.alloc_zero((size_t)n_groups * (size_t)e->ms, st));
+    DevBuf<float> tvals;
+    DevBuf<int32_t> trow, cursor, long_cols;
+    DevBuf<int> err, n_long;
+    DN_TRY(tvals.alloc((size_t)e->nnz));
+    DN_TRY(trow.alloc((size_t)e->nnz));
+    DN_TRY(cursor.alloc_zero((size_t)e->ms, st));
+    DN_TRY(long_cols.alloc((size_t)(col_last - col_first)));
     DN_TRY(err.alloc_zero(1, st));
+    DN_TRY(n_long.alloc_zero(1, st));
     trace.mark("  csc: scratch");
-    {
-        dim3 grid((unsigned)ceil_div(e->n, 8), (unsigned)n_seg);
-        k_csc_count<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->n, segs, rows_per_group, e->ms, cnt.p);
-        DN_LAUNCH_CHECK();
-        k_csc_group_bases<<<(unsigned)ceil_div(e->ms, 256), 256, 0, st>>>(cnt.p, n_groups, e->ms);
-        DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(2);
-    }
-    trace.mark("  csc: count");
-    for (int g = 0; g < n_groups; g++) {
-        const int64_t base = (int64_t)g * rows_per_group;
-        const int rows_in_group = (int)std::min<int64_t>(rows_per_group, e->n - base);
-        dim3 grid((unsigned)ceil_div(rows_in_group, 8), (unsigned)n_seg);
-        k_csc_mark<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, base, rows_in_group, segs, words, mask.p, err.p);
-        k_csc_place<<<grid, 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, base, rows_in_group, segs, words, mask.p,
-                                          e->c_colptr, cnt.p + (int64_t)g * e->ms, e->c_vals, e->c_row);
-        DN_COUNT_LAUNCH(2);
-        if (g + 1 < n_groups)
-            DN_CUDA(cudaMemsetAsync(mask.p, 0, sizeof(unsigned long long) * (size_t)e->ms * words, st));
+    for (int seg = seg_first; seg < seg_last; seg++) {
+        k_csc_scatter<<<(unsigned)ceil_div(e->n, 8), 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, e->n, segs, seg,
+                                                                  e->c_colptr, cursor.p, tvals.p, trow.p);
+        DN_COUNT_LAUNCH(1);
     }
     DN_LAUNCH_CHECK();
-    trace.mark("  csc: mark + place");
+    trace.mark("  csc: slots");
+    k_csc_list_long<<<(unsigned)ceil_div(col_last - col_first, 256), 256, 0, st>>>(e->c_colptr, col_first, col_last,
+                                                                                  long_cols.p, n_long.p);
+    DN_LAUNCH_CHECK();
+    int h_long = 0;
+    DN_CUDA(cudaMemcpyAsync(&h_long, n_long.p, sizeof(int), cudaMemcpyDeviceToHost, st));
+    DN_CUDA(cudaStreamSynchronize(st));
+    {
+        int64_t blocks = std::min<int64_t>(ceil_div(col_last - col_first, 8), (int64_t)kNumSMs * 32);
+        k_csc_order_short<<<(unsigned)blocks, 256, 0, st>>>(e->c_colptr, col_first, col_last, tvals.p, trow.p,
+                                                           e->c_vals, e->c_row, err.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(2);
+    }
+    if (h_long > 0) {
+        if (bitmap_bytes > 200 * 1024)
+            return fail(DNPEFF_ERR_UNSUPPORTED, "columns longer than 512 entries need n_rows <= 819200");
+        DN_CUDA(cudaFuncSetAttribute(k_csc_order_long, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bitmap_bytes));
+        int blocks = std::min(h_long, kNumSMs * 8);
+        k_csc_order_long<<<blocks, 256, bitmap_bytes, st>>>(e->c_colptr, long_cols.p, h_long, e->n, tvals.p, trow.p,
+                                                           e->c_vals, e->c_row, err.p);
+        DN_LAUNCH_CHECK();
+        DN_COUNT_LAUNCH(1);
+    }
+    trace.mark("  csc: row order");
     int herr = 0;
     DN_TRY(read_err_flag(err.p, st, &herr));
     if (herr) return data_error(herr);

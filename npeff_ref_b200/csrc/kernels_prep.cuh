@@ -257,22 +257,20 @@ __global__ void k_gather_counts(const int32_t* __restrict__ counts,
 }
 
 // ---- CSC build --------------------------------------------------------------
-// A stable transpose (rows ascending inside every column) without a sort.  Rows
-// are cut into groups of 64*words rows.  Pass 1 counts every column's entries per
-// group (integer atomics), pass 2 turns the counts into each group's first slot
-// inside the column, then group by group every column collects a bit mask of the
-// group rows that hold it (atomicOr: order-independent) and an entry's slot is
-// colptr + group base + popcount of the lower mask bits.  Deterministic, integer
-// atomics only.  cnt is [n_groups][n_cols], mask is [n_cols][words].
-// The bucketed rows are walked segment by segment: segment 0 is a row's popular
-// part, segment s >= 1 its entries in tail column block s-1 (tail_off[row][s-1] ..
-// tail_off[row][s]).  One warp per (row, segment), segments along grid.y so that
-// the passes run segment after segment: the masks, counts and CSC slots a segment
-// touches belong to one block of columns and stay in L2.
+// A transpose with rows ascending inside every column, in two steps.  (1) Every
+// entry takes the next free slot of its column (integer atomicAdd on a per-column
+// cursor) in a temporary copy of the CSC arrays: the columns are complete but in
+// arrival order.  This runs one launch per segment of the bucketed rows (segment
+// 0 = a row's popular part, segment s >= 1 = its entries in tail column block
+// s-1), so that the cursors and the slots being written belong to one block of
+// columns and stay in L2.  (2) Every column is put in row order into the final
+// arrays: a row occurs at most once per column, so the order -- and with it the
+// result -- does not depend on the arrival order.  Short columns are ranked by
+// comparison (keys in shared memory), long ones through a bitmap of their rows.
+// A row that holds a column twice shows up as two equal keys: kErrDuplicate.
 struct RowSegments {
     const uint32_t* tail_off;  // [rows][n_tail + 1]
     int stride;                // n_tail + 1
-    int first;                 // first segment the pass covers (grid.y = 0)
     __device__ void range(const int64_t* rowptr, int64_t row, int seg, int64_t& b, int64_t& e) const {
         const int64_t r0 = rowptr[row];
         const uint32_t* t = tail_off + row * stride;
@@ -281,67 +279,122 @@ struct RowSegments {
     }
 };
 
-// grid = (ceil(rows / 8), segments), 256 threads
-__global__ void k_csc_count(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                            int64_t n_rows, RowSegments segs, int rows_per_group, int64_t n_cols,
-                            int32_t* __restrict__ cnt) {
+// grid = ceil(rows / 8), 256 threads: one warp per row, segment `seg` of it
+__global__ void k_csc_scatter(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
+                              const float* __restrict__ vals, int64_t n_rows, RowSegments segs, int seg,
+                              const int64_t* __restrict__ colptr, int32_t* __restrict__ cursor,
+                              float* __restrict__ tvals, int32_t* __restrict__ trow) {
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= n_rows) return;
     int64_t beg, end;
-    segs.range(rowptr, row, segs.first + blockIdx.y, beg, end);
-    int32_t* c = cnt + (row / rows_per_group) * n_cols;
-    for (int64_t p = beg + (threadIdx.x & 31); p < end; p += 32) atomicAdd(c + colind[p], 1);
-}
-
-// cnt[g][j] <- sum of cnt[g'][j] over g' < g.
-__global__ void k_csc_group_bases(int32_t* __restrict__ cnt, int n_groups, int64_t n_cols) {
-    int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n_cols) return;
-    int32_t run = 0;
-    for (int g = 0; g < n_groups; g++) {
-        int32_t t = cnt[(int64_t)g * n_cols + j];
-        cnt[(int64_t)g * n_cols + j] = run;
-        run += t;
-    }
-}
-
-// grid = (ceil(rows of the group / 8), segments), 256 threads
-__global__ void k_csc_mark(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                           int64_t row_base, int rows_in_group, RowSegments segs, int words,
-                           unsigned long long* __restrict__ mask, int* __restrict__ err) {
-    const int rig = blockIdx.x * 8 + (threadIdx.x >> 5);  // row inside the group
-    if (rig >= rows_in_group) return;
-    int64_t beg, end;
-    segs.range(rowptr, row_base + rig, segs.first + blockIdx.y, beg, end);
-    const unsigned long long bit = 1ull << (rig & 63);
-    const int wi = rig >> 6;
-    for (int64_t p = beg + (threadIdx.x & 31); p < end; p += 32) {
-        unsigned long long old = atomicOr(mask + (int64_t)colind[p] * words + wi, bit);
-        if (old & bit) atomicOr(err, kErrDuplicate);
-    }
-}
-
-__global__ void k_csc_place(const int64_t* __restrict__ rowptr, const int32_t* __restrict__ colind,
-                            const float* __restrict__ vals, int64_t row_base, int rows_in_group,
-                            RowSegments segs, int words, const unsigned long long* __restrict__ mask,
-                            const int64_t* __restrict__ colptr, const int32_t* __restrict__ group_base,
-                            float* __restrict__ cvals, int32_t* __restrict__ crow) {
-    const int rig = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (rig >= rows_in_group) return;
-    const int64_t row = row_base + rig;
-    int64_t beg, end;
-    segs.range(rowptr, row, segs.first + blockIdx.y, beg, end);
-    const unsigned long long lower = (1ull << (rig & 63)) - 1ull;
-    const int wi = rig >> 6;
+    segs.range(rowptr, row, seg, beg, end);
     for (int64_t p = beg + (threadIdx.x & 31); p < end; p += 32) {
         const int32_t j = colind[p];
-        const unsigned long long* m = mask + (int64_t)j * words;
-        int rank = __popcll(m[wi] & lower);
-        for (int w = 0; w < wi; w++) rank += __popcll(m[w]);
-        const int64_t q = colptr[j] + group_base[j] + rank;
-        cvals[q] = vals[p];
-        crow[q] = (int32_t)row;
+        const int64_t q = colptr[j] + atomicAdd(cursor + j, 1);
+        tvals[q] = vals[p];
+        trow[q] = (int32_t)row;
     }
+}
+
+constexpr int kCscShortMax = 512;  // longest column ranked by comparison (keys per warp in shared memory)
+
+// Columns [col_first, col_last) with at most kCscShortMax entries: one warp per column.
+__global__ void __launch_bounds__(256)
+k_csc_order_short(const int64_t* __restrict__ colptr, int64_t col_first, int64_t col_last,
+                  const float* __restrict__ tvals, const int32_t* __restrict__ trow,
+                  float* __restrict__ cvals, int32_t* __restrict__ crow, int* __restrict__ err) {
+    __shared__ int32_t keys[8][kCscShortMax];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t warps = (int64_t)gridDim.x * 8;
+    for (int64_t j = col_first + (int64_t)blockIdx.x * 8 + w; j < col_last; j += warps) {
+        const int64_t b = colptr[j];
+        const int len = (int)(colptr[j + 1] - b);
+        if (len > kCscShortMax || len <= 0) continue;
+        if (len == 1) {
+            if (lane == 0) { cvals[b] = tvals[b]; crow[b] = trow[b]; }
+            continue;
+        }
+        for (int e = lane; e < len; e += 32) keys[w][e] = trow[b + e];
+        __syncwarp();
+        for (int e = lane; e < len; e += 32) {
+            const int32_t k = keys[w][e];
+            int rank = 0, same = 0;
+            for (int t = 0; t < len; t++) {
+                const int32_t o = keys[w][t];
+                rank += o < k;
+                same += o == k;
+            }
+            if (same > 1) atomicOr(err, kErrDuplicate);
+            // with a repeated row the ranks collide; keep the writes inside the column
+            crow[b + rank] = k;
+            cvals[b + rank] = tvals[b + e];
+        }
+        __syncwarp();
+    }
+}
+
+// Columns longer than kCscShortMax: one block per column, a bitmap of the column's
+// rows in shared memory (n_rows bits), rank = set bits below the row.
+// Dynamic shared memory: 2 * ceil(n_rows / 32) words.
+__global__ void __launch_bounds__(256)
+k_csc_order_long(const int64_t* __restrict__ colptr, const int32_t* __restrict__ long_cols, int n_long,
+                 int64_t n_rows, const float* __restrict__ tvals, const int32_t* __restrict__ trow,
+                 float* __restrict__ cvals, int32_t* __restrict__ crow, int* __restrict__ err) {
+    extern __shared__ uint32_t bm[];  // [words] bits, then [words] exclusive prefix of popcounts
+    const int words = (int)((n_rows + 31) / 32);
+    uint32_t* pre = bm + words;
+    __shared__ uint32_t carry;
+    for (int c = blockIdx.x; c < n_long; c += gridDim.x) {
+        const int64_t j = long_cols[c];
+        const int64_t b = colptr[j];
+        const int len = (int)(colptr[j + 1] - b);
+        for (int i = threadIdx.x; i < words; i += 256) bm[i] = 0u;
+        __syncthreads();
+        for (int e = threadIdx.x; e < len; e += 256) {
+            const int32_t k = trow[b + e];
+            const uint32_t bit = 1u << (k & 31);
+            if (atomicOr(bm + (k >> 5), bit) & bit) atomicOr(err, kErrDuplicate);
+        }
+        __syncthreads();
+        // exclusive prefix of the word popcounts, 256 words at a time
+        if (threadIdx.x == 0) carry = 0u;
+        __syncthreads();
+        for (int base = 0; base < words; base += 256) {
+            const int i = base + threadIdx.x;
+            uint32_t v = i < words ? (uint32_t)__popc(bm[i]) : 0u;
+            // block-wide inclusive scan of v (warp scans + warp totals)
+            uint32_t inc = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+                if ((threadIdx.x & 31) >= o) inc += t;
+            }
+            __shared__ uint32_t wtot[8];
+            if ((threadIdx.x & 31) == 31) wtot[threadIdx.x >> 5] = inc;
+            __syncthreads();
+            uint32_t add = carry;
+            for (int ww = 0; ww < (threadIdx.x >> 5); ww++) add += wtot[ww];
+            if (i < words) pre[i] = add + inc - v;
+            __syncthreads();
+            if (threadIdx.x == 255) carry = add + inc;
+            __syncthreads();
+        }
+        for (int e = threadIdx.x; e < len; e += 256) {
+            const int32_t k = trow[b + e];
+            const int rank = (int)(pre[k >> 5] + (uint32_t)__popc(bm[k >> 5] & ((1u << (k & 31)) - 1u)));
+            crow[b + rank] = k;
+            cvals[b + rank] = tvals[b + e];
+        }
+        __syncthreads();
+    }
+}
+
+// long_cols <- ids of the columns in [col_first, col_last) longer than kCscShortMax.
+__global__ void k_csc_list_long(const int64_t* __restrict__ colptr, int64_t col_first, int64_t col_last,
+                                int32_t* __restrict__ long_cols, int* __restrict__ n_long) {
+    int64_t j = col_first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= col_last) return;
+    if (colptr[j + 1] - colptr[j] > kCscShortMax) long_cols[atomicAdd(n_long, 1)] = (int32_t)j;
 }
 
 // ---- internal column order and row buckets -----------------------------------
