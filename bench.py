@@ -1,5 +1,5 @@
 """D-NPEFF NMF benchmark: iterations/s of the multiplicative-update loop and the
-HBM roofline of its dominant kernel, on synthetic D-PEFs of BASELINE config 2
+HBM roofline of its dominant kernel, on synthetic D-PEFs of the headline workload, configuration 2
 (n=20,000 examples, m=4,194,304 features, 32,768 stored values per row, r=128).
 
     python bench.py --gpus N --steps K --warmup W            # this engine
@@ -30,7 +30,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CONFIGS = {
-    # name: n, m, k, r, alpha, sigma, seed   (BASELINE.json configs, 1-based)
+    # name: n, m, k, r, alpha, sigma, seed   (the benchmark's workload configurations, 1-based)
     1: dict(n=2048, m=65536, k=4096, r=32, alpha=1.1, sigma=1.0, seed=0),
     2: dict(n=20000, m=4194304, k=32768, r=128, alpha=1.1, sigma=1.0, seed=1),
     3: dict(n=50000, m=16777216, k=65536, r=256, alpha=1.1, sigma=1.0, seed=2),

@@ -560,13 +560,15 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             DN_CUDA(cudaMalloc((void**)&e->blk_partial,
                                sizeof(float) * std::max(e->plan_x1.partial_floats, e->plan_x2.partial_floats)));
             DN_CUDA(cudaMemsetAsync(e->x1, 0, sizeof(float) * e->plan_x1.x_floats, st));
-            DN_CUDA(cudaMemsetAsync(e->x2, 0, sizeof(float) * e->plan_x2.x_floats, st));
             int64_t blocks = std::min<int64_t>(ceil_div(n, 8), (int64_t)kNumSMs * 16);
             k_fill_blocks<<<(unsigned)blocks, 256, 0, st>>>(e->b_vals, e->b_col, e->a_rowptr, e->tail_off,
-                                                           (int)(nb + 1), n, e->plan_x1.k_chunks,
-                                                           e->plan_x2.k_chunks, e->x1, e->x2);
+                                                           (int)(nb + 1), n, e->plan_x1.k_chunks, e->x1);
             DN_LAUNCH_CHECK();
-            DN_COUNT_LAUNCH(1);
+            dim3 tgrid((unsigned)e->plan_x1.m_tiles, (unsigned)e->plan_x2.m_tiles);
+            k_block_transpose<<<tgrid, 256, 0, st>>>(e->x1, e->plan_x1.m_tiles, e->plan_x1.k_chunks, e->x2,
+                                                    e->plan_x2.m_tiles, e->plan_x2.k_chunks);
+            DN_LAUNCH_CHECK();
+            DN_COUNT_LAUNCH(2);
         }
         trace.mark("dense popular block");
         // stored entries per tail block (decides warp-per-row or block-per-row launches)

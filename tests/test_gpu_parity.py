@@ -257,7 +257,7 @@ def test_op_block_product_matches_float64(torch_cuda, M, K, r):
 CASES = [
     # n, m, k, r, iters, eps
     (64, 700, 40, 8, 50, 1e-12),
-    (256, 6000, 300, 32, 50, 1e-12),     # BASELINE config 1's shape, scaled down 8x
+    (256, 6000, 300, 32, 50, 1e-12),     # configuration 1's shape, scaled down 8x
     (96, 9000, 1500, 128, 50, 1e-8),     # long rows (block kernel), r = 128 > n: near-exact fit
     (300, 9000, 1500, 128, 50, 1e-12),   # long rows, r = 128 < n
     (80, 3000, 200, 20, 30, 1e-8),       # rank not a power of two
