@@ -24,10 +24,48 @@ using namespace dnpeff;
 
 namespace {
 
+// While a PoolScope is alive on this thread, DevBuf takes its memory from the
+// device's stream-ordered pool on that stream: cudaFree waits for every stream of
+// the device -- also for an upload that is meant to overlap the loader -- whereas
+// cudaFreeAsync only orders the release behind the work queued so far.
+struct PoolScope {
+    static thread_local cudaStream_t stream;
+    static thread_local int depth;
+    int device = 0;
+    explicit PoolScope(cudaStream_t st) {
+        if (depth++ == 0) {
+            stream = st;
+            cudaGetDevice(&device);
+            cudaMemPool_t pool;
+            if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+                uint64_t keep = UINT64_MAX;  // no release to the OS in the middle of the work
+                cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+            }
+        }
+    }
+    ~PoolScope() {
+        if (--depth == 0) {
+            cudaStreamSynchronize(stream);
+            cudaMemPool_t pool;
+            if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+                uint64_t keep = 0;
+                cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+                cudaMemPoolTrimTo(pool, 0);  // the temporaries go back to the device
+            }
+            stream = nullptr;
+        }
+    }
+    static bool active() { return depth > 0; }
+};
+thread_local cudaStream_t PoolScope::stream = nullptr;
+thread_local int PoolScope::depth = 0;
+
 template <typename T>
 struct DevBuf {
     T* p = nullptr;
     size_t count = 0;
+    bool pooled = false;
+    cudaStream_t pool_stream = nullptr;
     DevBuf() {}
     DevBuf(const DevBuf&) = delete;
     DevBuf& operator=(const DevBuf&) = delete;
@@ -35,7 +73,16 @@ struct DevBuf {
     int alloc(size_t n) {
         release();
         count = n;
-        DN_CUDA(cudaMalloc((void**)&p, sizeof(T) * (n ? n : 1)));
+        // (large buffers stay with cudaMalloc: growing and trimming the pool by
+        // gigabytes costs far more than the synchronisation it avoids)
+        if (PoolScope::active() && sizeof(T) * n <= ((size_t)64 << 20)) {
+            pooled = true;
+            pool_stream = PoolScope::stream;
+            DN_CUDA(cudaMallocAsync((void**)&p, sizeof(T) * (n ? n : 1), pool_stream));
+        } else {
+            pooled = false;
+            DN_CUDA(cudaMalloc((void**)&p, sizeof(T) * (n ? n : 1)));
+        }
         return DNPEFF_OK;
     }
     int alloc_zero(size_t n, cudaStream_t st) {
@@ -44,7 +91,10 @@ struct DevBuf {
         return DNPEFF_OK;
     }
     void release() {
-        if (p) cudaFree(p);
+        if (p) {
+            if (pooled) cudaFreeAsync(p, pool_stream);
+            else cudaFree(p);
+        }
         p = nullptr;
         count = 0;
     }
@@ -144,6 +194,7 @@ struct dnpeff_engine {
     float* tc_scratch = nullptr;  // 2*r*r: the update's small matrix split for the tensor cores
     double* red_partial = nullptr;  // device, 2*kRedBlocks doubles
     double* red_out = nullptr;      // device, 4 doubles
+    void* h_pinned = nullptr;       // 256 bytes of page-locked host memory for scalar read-backs
     SpmmPlan plan_csr, plan_csc;
 
     double a_sq = 0.0, a_sum = 0.0;
@@ -293,6 +344,20 @@ void free_matrix(dnpeff_engine* e) {
     e->a_sq_global = -1.0;
 }
 
+// Small device -> host read through the engine's page-locked scratch: a copy into
+// pageable memory would queue behind a large upload that is still in flight.
+int read_small(dnpeff_engine* e, const void* dptr, size_t bytes, void* out) {
+    if (bytes > 256 || !e->h_pinned) {
+        DN_CUDA(cudaMemcpyAsync(out, dptr, bytes, cudaMemcpyDeviceToHost, e->st));
+        DN_CUDA(cudaStreamSynchronize(e->st));
+        return DNPEFF_OK;
+    }
+    DN_CUDA(cudaMemcpyAsync(e->h_pinned, dptr, bytes, cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    memcpy(out, e->h_pinned, bytes);
+    return DNPEFF_OK;
+}
+
 int read_err_flag(int* d_err, cudaStream_t st, int* host) {
     DN_CUDA(cudaMemcpyAsync(host, d_err, sizeof(int), cudaMemcpyDeviceToHost, st));
     DN_CUDA(cudaStreamSynchronize(st));
@@ -324,13 +389,13 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         return fail(DNPEFF_ERR_UNSUPPORTED, "n_rows and n_cols_full must fit int32");
     cudaStream_t st = e->st;
     free_matrix(e);
+    PoolScope pool_scope(st);
     const int r = e->p.rank;
 
     int64_t nnz_in = n * k;
     if (d_rowptr) {
         if (n > 0) {
-            DN_CUDA(cudaMemcpyAsync(&nnz_in, d_rowptr + n, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-            DN_CUDA(cudaStreamSynchronize(st));
+            DN_TRY(read_small(e, d_rowptr + n, sizeof(int64_t), &nnz_in));
         } else {
             nnz_in = 0;
         }
@@ -353,7 +418,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
     }
-    DN_TRY(read_err_flag(err.p, st, &herr));
+    DN_TRY(read_small(e, err.p, sizeof(int), &herr));
     if (herr) return data_error(herr);
 
     trace.mark("count columns");
@@ -382,8 +447,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             DN_COUNT_LAUNCH(1);
         }
         DN_TRY(scan_exclusive<int32_t>(flags.p, pos.p, m_full + 1, st));
-        DN_CUDA(cudaMemcpyAsync(&m_kept, pos.p + m_full, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-        DN_CUDA(cudaStreamSynchronize(st));
+        DN_TRY(read_small(e, pos.p + m_full, sizeof(int64_t), &m_kept));
         DN_CUDA(cudaMalloc((void**)&e->new_to_og, sizeof(int32_t) * (size_t)std::max<int64_t>(m_kept, 1)));
         if (m_full > 0) {
             k_build_maps<<<(unsigned)ceil_div(m_full, 256), 256, 0, st>>>(flags.p, pos.p, m_full,
@@ -420,8 +484,8 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     }
     DN_TRY(scan_exclusive<int32_t>(row_count.p, e->a_rowptr, n + 1, st));
     int64_t nnz = 0;
-    DN_CUDA(cudaMemcpyAsync(&nnz, e->a_rowptr + n, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-    DN_TRY(read_err_flag(err.p, st, &herr));
+    DN_TRY(read_small(e, e->a_rowptr + n, sizeof(int64_t), &nnz));
+    DN_TRY(read_small(e, err.p, sizeof(int), &herr));
     if (herr) return data_error(herr);
 
     trace.mark("row counts + scan");
@@ -461,8 +525,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DN_COUNT_LAUNCH(1);
     DN_TRY(scan_exclusive<int32_t>(hot_flags.p, hot_pos.p, ms + 1, st));
     int64_t n_hot = 0;
-    DN_CUDA(cudaMemcpyAsync(&n_hot, hot_pos.p + ms, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-    DN_CUDA(cudaStreamSynchronize(st));
+    DN_TRY(read_small(e, hot_pos.p + ms, sizeof(int64_t), &n_hot));
     int64_t max_hot = (int64_t)kMaxHotTiles * tile;
     if (dense) {
         // both dense copies (8 bytes per element of the block) within a third of
@@ -494,8 +557,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
         DN_TRY(scan_exclusive<int32_t>(hot_flags.p, hot_pos.p, ms + 1, st));
-        DN_CUDA(cudaMemcpyAsync(&n_hot, hot_pos.p + ms, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-        DN_CUDA(cudaStreamSynchronize(st));
+        DN_TRY(read_small(e, hot_pos.p + ms, sizeof(int64_t), &n_hot));
     }
     DN_CUDA(cudaMalloc((void**)&e->perm, sizeof(int32_t) * (size_t)std::max<int64_t>(ms, 1)));
     DN_CUDA(cudaMalloc((void**)&e->inv_perm, sizeof(int32_t) * (size_t)std::max<int64_t>(ms, 1)));
@@ -577,9 +639,8 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         for (int64_t b = 0; b < nb; b++) {
             int64_t lo = n_hot + b * block, hi = std::min<int64_t>(ms, lo + block);
             int64_t v[2];
-            DN_CUDA(cudaMemcpyAsync(&v[0], e->c_colptr + lo, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-            DN_CUDA(cudaMemcpyAsync(&v[1], e->c_colptr + hi, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
-            DN_CUDA(cudaStreamSynchronize(st));
+            DN_TRY(read_small(e, e->c_colptr + lo, sizeof(int64_t), &v[0]));
+            DN_TRY(read_small(e, e->c_colptr + hi, sizeof(int64_t), &v[1]));
             e->tail_nnz[(size_t)b] = v[1] - v[0];
         }
     }
@@ -628,6 +689,7 @@ int fill_csc(dnpeff_engine* e, int mode) {
     if (seg_first >= seg_last || col_first >= col_last) return DNPEFF_OK;
     RowSegments segs = {e->tail_off, e->n_tail_blocks + 1};
     const size_t bitmap_bytes = 2 * (size_t)ceil_div(e->n, 32) * sizeof(uint32_t);
+    PoolScope pool_scope(st);
     PhaseTrace trace(st);
     DevBuf<float> tvals;
     DevBuf<int32_t> trow, cursor, long_cols;
@@ -1011,6 +1073,10 @@ int dnpeff_create(const dnpeff_params* params, int device, void* stream, dnpeff_
         dnpeff_destroy(e);
         return fail(DNPEFF_ERR_CUDA, "cudaMalloc of reduction buffers failed");
     }
+    if (cudaHostAlloc(&e->h_pinned, 256, cudaHostAllocDefault) != cudaSuccess) {
+        e->h_pinned = nullptr;  // read_small falls back to pageable copies
+        cudaGetLastError();
+    }
     e->launches0 = launch_counter();
     *out = e;
     return DNPEFF_OK;
@@ -1024,6 +1090,8 @@ int dnpeff_destroy(dnpeff_engine* e) {
     free_matrix(e);
     dev_free(e->red_partial);
     dev_free(e->red_out);
+    if (e->h_pinned) cudaFreeHost(e->h_pinned);
+    e->h_pinned = nullptr;
     dev_free(e->work_counter);
     dev_free(e->d_err);
     for (auto& r : e->regions) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
@@ -1077,6 +1145,7 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
     if (nnz < 0) return fail(DNPEFF_ERR_DATA, "negative nnz");
     if (nnz > 0 && (!vals || !colind)) return fail(DNPEFF_ERR_INVALID, "null vals/colind");
     free_matrix(e);
+    PoolScope pool_scope(e->st);
     DevBuf<float> dv, dn;
     DevBuf<int32_t> dc;
     DevBuf<int64_t> dr;
