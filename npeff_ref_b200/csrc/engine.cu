@@ -378,11 +378,20 @@ void shard_range(int64_t total, int n_shards, int idx, int64_t* start, int64_t* 
     *size = (idx == n_shards - 1) ? base + total % n_shards : base;
 }
 
+// The values may arrive in slabs of rows (a host upload still in flight): rows
+// [row_end[s-1], row_end[s]) are valid once ready[s] has fired.  Everything that
+// needs the column ids only runs before the first wait.
+struct LoadSlabs {
+    int count = 0;
+    int64_t row_end[8];
+    cudaEvent_t ready[8];
+};
+
 // d_retained != nullptr: the kept columns are that list of original ids (device
 // pointer, n_retained of them) instead of the columns with >= min_count entries.
 int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const int64_t* d_rowptr,
                 const float* d_vals, const int32_t* d_col, const float* d_norms, int32_t min_count,
-                const int32_t* d_retained = nullptr, int64_t n_retained = 0, cudaEvent_t vals_ready = nullptr) {
+                const int32_t* d_retained = nullptr, int64_t n_retained = 0, const LoadSlabs* slabs = nullptr) {
     if (n < 0 || m_full < 0 || (d_rowptr == nullptr && k < 0))
         return fail(DNPEFF_ERR_INVALID, "negative shape");
     if (n >= INT32_MAX || m_full >= INT32_MAX)
@@ -489,22 +498,10 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     if (herr) return data_error(herr);
 
     trace.mark("row counts + scan");
-    // (the values may still be on their way from the host: everything up to here
-    // needed the column ids only)
-    if (vals_ready) DN_CUDA(cudaStreamWaitEvent(st, vals_ready, 0));
-    // 5. order-preserving extraction with the row normalisation applied
+    // 5. (the order-preserving extraction needs the values and comes further down,
+    //    slab by slab; everything up to there needs the column ids only)
     DN_CUDA(cudaMalloc((void**)&e->a_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
     DN_CUDA(cudaMalloc((void**)&e->a_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
-    if (n > 0) {
-        int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 32);
-        k_extract_shard<<<(unsigned)blocks, 256, 0, st>>>(d_vals, d_col, d_rowptr, k, n, d_norms,
-                                                         og_to_new.p, map, e->a_rowptr,
-                                                         e->a_vals, e->a_col);
-        DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(1);
-    }
-
-    trace.mark("extract shard");
     // 6. internal column order: popular columns first (they get the tiled,
     //    shared-memory kernels), then the rest; both parts in local-id order
     DevBuf<int32_t> cnt_s, hot_flags, cnt_p;
@@ -603,15 +600,6 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         DN_CUDA(cudaMalloc((void**)&e->b_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
         DN_CUDA(cudaMalloc((void**)&e->b_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
         DN_CUDA(cudaMalloc((void**)&e->tail_off, sizeof(uint32_t) * (size_t)std::max<int64_t>(n * (nb + 1), 1)));
-        if (n > 0) {
-            size_t smem = sizeof(int) * 8 * (size_t)std::max(bm.n_buckets, 1);
-            int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 16);
-            k_bucket_rows<<<(unsigned)blocks, 256, smem, st>>>(e->a_vals, e->a_col, e->a_rowptr, n, e->inv_perm,
-                                                              bm, e->b_vals, e->b_col, e->tail_off);
-            DN_LAUNCH_CHECK();
-            DN_COUNT_LAUNCH(1);
-        }
-        trace.mark("bucket rows");
         if (dense) {
             e->plan_x1 = block_tc_plan(n, n_hot, r);
             e->plan_x2 = block_tc_plan(n_hot, n, r);
@@ -622,17 +610,43 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             DN_CUDA(cudaMalloc((void**)&e->blk_partial,
                                sizeof(float) * std::max(e->plan_x1.partial_floats, e->plan_x2.partial_floats)));
             DN_CUDA(cudaMemsetAsync(e->x1, 0, sizeof(float) * e->plan_x1.x_floats, st));
-            int64_t blocks = std::min<int64_t>(ceil_div(n, 8), (int64_t)kNumSMs * 16);
-            k_fill_blocks<<<(unsigned)blocks, 256, 0, st>>>(e->b_vals, e->b_col, e->a_rowptr, e->tail_off,
-                                                           (int)(nb + 1), n, e->plan_x1.k_chunks, e->x1);
+        }
+        trace.mark("index-only phases done");
+        // slab by slab, as the values arrive: extraction with the row normalisation
+        // applied, bucketing of the rows, the dense copy of the popular part
+        const int n_slabs = slabs ? slabs->count : 1;
+        int64_t row0 = 0;
+        for (int sl = 0; sl < n_slabs && n > 0; sl++) {
+            const int64_t row1 = slabs ? slabs->row_end[sl] : n;
+            if (slabs) DN_CUDA(cudaStreamWaitEvent(st, slabs->ready[sl], 0));
+            if (row1 <= row0) continue;
+            const int64_t rows = row1 - row0;
+            k_extract_shard<<<(unsigned)std::min<int64_t>(rows, (int64_t)kNumSMs * 32), 256, 0, st>>>(
+                d_vals, d_col, d_rowptr, k, row0, row1, d_norms, og_to_new.p, map, e->a_rowptr, e->a_vals, e->a_col);
             DN_LAUNCH_CHECK();
+            size_t smem = sizeof(int) * 8 * (size_t)std::max(bm.n_buckets, 1);
+            k_bucket_rows<<<(unsigned)std::min<int64_t>(rows, (int64_t)kNumSMs * 16), 256, smem, st>>>(
+                e->a_vals, e->a_col, e->a_rowptr, row0, row1, e->inv_perm, bm, e->b_vals, e->b_col, e->tail_off);
+            DN_LAUNCH_CHECK();
+            DN_COUNT_LAUNCH(2);
+            if (dense) {
+                k_fill_blocks<<<(unsigned)std::min<int64_t>(ceil_div(rows, 8), (int64_t)kNumSMs * 16), 256, 0, st>>>(
+                    e->b_vals, e->b_col, e->a_rowptr, e->tail_off, (int)(nb + 1), row0, row1, e->plan_x1.k_chunks,
+                    e->x1);
+                DN_LAUNCH_CHECK();
+                DN_COUNT_LAUNCH(1);
+            }
+            row0 = row1;
+        }
+        trace.mark("extract, bucket, dense fill");
+        if (dense) {
             dim3 tgrid((unsigned)e->plan_x1.m_tiles, (unsigned)e->plan_x2.m_tiles);
             k_block_transpose<<<tgrid, 256, 0, st>>>(e->x1, e->plan_x1.m_tiles, e->plan_x1.k_chunks, e->x2,
                                                     e->plan_x2.m_tiles, e->plan_x2.k_chunks);
             DN_LAUNCH_CHECK();
-            DN_COUNT_LAUNCH(2);
+            DN_COUNT_LAUNCH(1);
         }
-        trace.mark("dense popular block");
+        trace.mark("transposed dense block");
         // stored entries per tail block (decides warp-per-row or block-per-row launches)
         std::vector<int64_t> colptr_h;
         e->tail_nnz.assign((size_t)nb, 0);
@@ -1151,29 +1165,42 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
     DevBuf<int64_t> dr;
     DN_TRY(dv.alloc((size_t)nnz));
     DN_TRY(dc.alloc((size_t)nnz));
-    // The column ids go first, on the engine's stream; the values (and norms) follow on
-    // a second stream, so that counting, pruning and the row offsets overlap their upload.
+    // The column ids go first, on the engine's stream; the values follow on a second
+    // stream in slabs of rows, so that counting, pruning, row offsets and the column
+    // permutation overlap their upload and every slab is processed as it lands.
     cudaStream_t up = nullptr;
-    cudaEvent_t vals_ready = nullptr;
+    LoadSlabs slabs;
     struct UploadGuard {
         cudaStream_t& s;
-        cudaEvent_t& ev;
+        LoadSlabs& sl;
         ~UploadGuard() {
             if (s) { cudaStreamSynchronize(s); cudaStreamDestroy(s); }
-            if (ev) cudaEventDestroy(ev);
+            for (int i = 0; i < sl.count; i++) cudaEventDestroy(sl.ready[i]);
         }
-    } upload_guard{up, vals_ready};
+    } upload_guard{up, slabs};
     if (nnz > 0) {
         DN_CUDA(cudaMemcpyAsync(dc.p, colind, sizeof(int32_t) * (size_t)nnz, cudaMemcpyHostToDevice, e->st));
         DN_CUDA(cudaStreamCreateWithFlags(&up, cudaStreamNonBlocking));
-        DN_CUDA(cudaEventCreateWithFlags(&vals_ready, cudaEventDisableTiming));
         // the copy engine takes the transfers in issue order: ids first
         cudaEvent_t ids_issued = nullptr;
         DN_CUDA(cudaEventCreateWithFlags(&ids_issued, cudaEventDisableTiming));
         DN_CUDA(cudaEventRecord(ids_issued, e->st));
         DN_CUDA(cudaStreamWaitEvent(up, ids_issued, 0));
         cudaEventDestroy(ids_issued);
-        DN_CUDA(cudaMemcpyAsync(dv.p, vals, sizeof(float) * (size_t)nnz, cudaMemcpyHostToDevice, up));
+        const int n_slabs = nnz >= ((int64_t)64 << 20) ? 4 : 1;
+        int64_t off0 = 0;
+        for (int i = 0; i < n_slabs; i++) {
+            const int64_t row1 = i + 1 == n_slabs ? n_rows : n_rows * (i + 1) / n_slabs;
+            const int64_t off1 = rowptr ? rowptr[row1] : row1 * k_per_row;
+            if (off1 > off0)
+                DN_CUDA(cudaMemcpyAsync(dv.p + off0, vals + off0, sizeof(float) * (size_t)(off1 - off0),
+                                        cudaMemcpyHostToDevice, up));
+            DN_CUDA(cudaEventCreateWithFlags(&slabs.ready[i], cudaEventDisableTiming));
+            slabs.count = i + 1;
+            slabs.row_end[i] = row1;
+            DN_CUDA(cudaEventRecord(slabs.ready[i], up));
+            off0 = off1;
+        }
     }
     if (rowptr) {
         DN_TRY(dr.alloc((size_t)n_rows + 1));
@@ -1184,7 +1211,6 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
         if (n_rows > 0)
             DN_CUDA(cudaMemcpyAsync(dn.p, norms, sizeof(float) * (size_t)n_rows, cudaMemcpyHostToDevice, e->st));
     }
-    if (vals_ready) DN_CUDA(cudaEventRecord(vals_ready, up));
     DevBuf<int32_t> dret;
     if (retained) {
         DN_TRY(dret.alloc((size_t)std::max<int64_t>(n_retained, 1)));
@@ -1193,7 +1219,7 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
     }
     int s = load_device(e, n_rows, n_cols_full, k_per_row, rowptr ? dr.p : nullptr, dv.p, dc.p,
                         norms ? dn.p : nullptr, min_values_per_parameter, retained ? dret.p : nullptr, n_retained,
-                        vals_ready);
+                        slabs.count > 0 ? &slabs : nullptr);
     if (s != DNPEFF_OK) free_matrix(e);
     cudaStreamSynchronize(e->st);
     return s;

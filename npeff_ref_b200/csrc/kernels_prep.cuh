@@ -196,14 +196,14 @@ __global__ void k_row_counts(const int32_t* __restrict__ colind, const int64_t* 
 // the way and the column ids rebased to the shard start
 // (src/util/matrix_util.h:57-61).  One block of 256 threads per row.
 __global__ void k_extract_shard(const float* __restrict__ vals, const int32_t* __restrict__ colind,
-                                const int64_t* __restrict__ rowptr, int64_t k, int64_t n_rows,
+                                const int64_t* __restrict__ rowptr, int64_t k, int64_t row_begin, int64_t n_rows,
                                 const float* __restrict__ norms,
                                 const int32_t* __restrict__ og_to_new, ShardMap map,
                                 const int64_t* __restrict__ out_rowptr, float* __restrict__ out_vals,
                                 int32_t* __restrict__ out_colind) {
     __shared__ int wtot[8];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    for (int64_t row = row_begin + blockIdx.x; row < n_rows; row += gridDim.x) {
         int64_t b, e;
         row_range(rowptr, k, row, b, e);
         if (e < b) e = b;
@@ -443,14 +443,15 @@ struct BucketMap {
 // the hot part; n_tail_blocks + 1 entries per row).
 __global__ void __launch_bounds__(256)
 k_bucket_rows(const float* __restrict__ vals, const int32_t* __restrict__ col,
-              const int64_t* __restrict__ rowptr, int64_t n_rows, const int32_t* __restrict__ inv_perm,
+              const int64_t* __restrict__ rowptr, int64_t row_begin, int64_t n_rows,
+              const int32_t* __restrict__ inv_perm,
               BucketMap bm, float* __restrict__ out_vals, int32_t* __restrict__ out_col,
               uint32_t* __restrict__ tail_off) {
     extern __shared__ int cnt[];  // [8][n_buckets]
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int NB = bm.n_buckets;
     const int n_tail = NB - bm.n_hot_tiles;
-    for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+    for (int64_t row = row_begin + blockIdx.x; row < n_rows; row += gridDim.x) {
         const int64_t beg = rowptr[row], end = rowptr[row + 1];
         const int64_t len = end - beg;
         int64_t chunk = ((len + 7) / 8 + 31) / 32 * 32;  // per-warp share, a multiple of 32
