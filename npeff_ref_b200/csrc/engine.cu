@@ -32,12 +32,15 @@ struct PoolScope {
     static thread_local cudaStream_t stream;
     static thread_local int depth;
     int device = 0;
+    uint64_t saved_threshold = 0;
+    bool have_saved = false;
     explicit PoolScope(cudaStream_t st) {
         if (depth++ == 0) {
             stream = st;
             cudaGetDevice(&device);
             cudaMemPool_t pool;
             if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+                have_saved = cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &saved_threshold) == cudaSuccess;
                 uint64_t keep = UINT64_MAX;  // no release to the OS in the middle of the work
                 cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
             }
@@ -48,9 +51,10 @@ struct PoolScope {
             cudaStreamSynchronize(stream);
             cudaMemPool_t pool;
             if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
-                uint64_t keep = 0;
-                cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
-                cudaMemPoolTrimTo(pool, 0);  // the temporaries go back to the device
+                // the pool gets the caller's setting back; what this scope parked in it
+                // goes back to the device unless the caller wants memory kept
+                if (have_saved) cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &saved_threshold);
+                if (!have_saved || saved_threshold == 0) cudaMemPoolTrimTo(pool, 0);
             }
             stream = nullptr;
         }
