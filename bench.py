@@ -41,12 +41,13 @@ METRIC = "dnpeff_nmf_iterations_per_s"
 UNIT = "iter/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one A*H^T product (a sequence of
-# launches: one tiled + one per tail column block), keyed by (config, ranks, product).
-# Config 2 on one GPU: scaled from an ncu capture of the same workload with a tenth
-# of the rows (2.68 GB measured against 2.53 GB algorithmic = 1.06x): the part that
-# grows with the stored entries (8 B each) is scaled by the entry count, the dense
-# factor is read once either way: 2.68e9 + 1.06 * 8 * (655.36e6 - 65.54e6).
-NCU_TRAFFIC_BYTES = {(2, 1, "spmm_ah"): 7.7e9}
+# launches: the dense popular block on tensor cores + one launch per tail column
+# block), keyed by (config, ranks, product).  Config 2 on one GPU: scaled from an ncu
+# capture of the same workload with a tenth of the rows, where the product moved
+# 3.06 GB: 2.01 GB are the dense factor H, read once whatever the row count; the
+# other 1.05 GB (dense block of A, tail entries, split-K partials) grow with the
+# rows: 2.15e9 (H at full size) + 10 * 1.05e9.
+NCU_TRAFFIC_BYTES = {(2, 1, "spmm_ah"): 12.6e9}
 
 
 def workload_name(cfg_id, c):
@@ -344,7 +345,7 @@ def main():
         "traffic": NCU_TRAFFIC_BYTES.get((cfg_id, world, dom)),
         "algorithmic_bytes_per_launch": spmm_bytes,
         "ms_per_launch": {a: (round(b, 4) if b is not None else None) for a, b in per_kernel.items()},
-        "note": "one product = one tiled launch + one launch per tail column block, timed as a whole; "
+        "note": "one product = the dense popular block on tensor cores + one launch per tail column block, timed as a whole; "
                 "every stored entry gathers r floats on chip (shared memory or L2), so the SpMM is not "
                 "HBM-bound for r >= 64; traffic is scaled from a small-case capture",
     }
