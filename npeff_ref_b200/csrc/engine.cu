@@ -310,20 +310,36 @@ int hot_divisor(bool dense) {
 // G = X^T X: tcgen05 kernel where the rank allows, CUDA-core kernel otherwise.
 int gram_any(const float* X, int64_t rows, int r, float* G, float* scratch, int* err, cudaStream_t st) {
     if (tensor_cores_enabled() && gram_tc_ok(r)) return gram_blk_launch(X, rows, r, G, scratch, err, st);
+    if (tensor_cores_enabled() && gram_wide_ok(r) && rows > 0) return gram_wide_launch(X, rows, r, G, scratch, err, st);
     return gram_launch(X, rows, r, G, scratch, st);
 }
 
 size_t gram_any_scratch(int64_t rows, int r) {
     size_t a = gram_plan(rows, r).scratch_floats;
     size_t b = gram_tc_ok(r) ? gram_blk_plan(rows).scratch_floats : 0;
+    if (gram_wide_ok(r)) b = gram_wide_plan(rows, r).scratch_floats;
     return a > b ? a : b;
 }
 
 // tc_scratch: 2*r*r floats.
+// num_is_scratch: the caller does not need Num after the call (the wide-rank kernel
+// cannot update X in place and then writes its result over Num before copying it back).
 int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int r, float eps,
-                  float* tc_scratch, int* err, cudaStream_t st) {
+                  float* tc_scratch, int* err, cudaStream_t st, bool num_is_scratch = false) {
     if (tensor_cores_enabled() && mu_update_tc_ok(r))
         return mu_update_tc_launch(X, Num, G, rows, r, eps, tc_scratch, err, st);
+    if (tensor_cores_enabled() && mu_update_wide_ok(r) && rows > 0) {
+        DevBuf<float> tmp;
+        float* out = const_cast<float*>(Num);
+        if (!num_is_scratch) {
+            DN_TRY(tmp.alloc((size_t)(rows * r)));
+            out = tmp.p;
+        }
+        DN_TRY(mu_update_wide_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
+        DN_CUDA(cudaMemcpyAsync(X, out, sizeof(float) * (size_t)(rows * r), cudaMemcpyDeviceToDevice, st));
+        if (!num_is_scratch) DN_CUDA(cudaStreamSynchronize(st));  // tmp is released on return
+        return DNPEFF_OK;
+    }
     return mu_update_launch(X, Num, G, rows, r, eps, st);
 }
 
@@ -904,7 +920,7 @@ int step_h(dnpeff_engine* e) {
         DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st));
     }
     ScopedTimer t(e, 3);
-    return mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st);
+    return mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st, true);
 }
 
 int global_a_sq(dnpeff_engine* e, double* out) {

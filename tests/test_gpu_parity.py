@@ -81,7 +81,7 @@ def test_op_spmm_matches_oracle(torch_cuda, r):
 
 
 @pytest.mark.parametrize("rows,r", [(1, 4), (1000, 32), (5000, 64), (777, 48), (20000, 128),
-                                    (3001, 256), (2500, 512), (100, 5), (0, 16)])
+                                    (3001, 256), (2500, 512), (40007, 384), (100, 5), (0, 16), (0, 256), (1, 256), (65, 512)])
 def test_op_gram_matches_oracle(torch_cuda, rows, r):
     from npeff_ref_b200._lib import lib, check
     torch = torch_cuda
@@ -100,7 +100,7 @@ def test_op_gram_matches_oracle(torch_cuda, rows, r):
 
 
 @pytest.mark.parametrize("rows,r", [(1, 4), (513, 32), (300, 64), (1000, 48), (4099, 128),
-                                    (700, 256), (200, 512), (50, 5), (64, 516)])
+                                    (700, 256), (200, 512), (3000, 384), (50, 5), (64, 516)])
 def test_op_mu_update_matches_oracle(torch_cuda, rows, r):
     from npeff_ref_b200._lib import lib, check
     torch = torch_cuda
@@ -262,6 +262,7 @@ CASES = [
     (300, 9000, 1500, 128, 50, 1e-12),   # long rows, r = 128 < n
     (80, 3000, 200, 20, 30, 1e-8),       # rank not a power of two
     (50, 400, 30, 7, 20, 1e-8),          # odd rank: generic kernels
+    (300, 6000, 800, 256, 20, 1e-12),    # wide rank: the panelled tensor-core update kernel
 ]
 
 
@@ -296,10 +297,12 @@ def test_full_run_matches_oracle(torch_cuda, n, m, k, r, iters, eps):
         assert rel_fro(H, Ho) < 1e-4, rel_fro(H, Ho)
         l = eng.compute_uncached_loss()
         # The loss is sqrt(|A|^2 + pos - 2 neg): its squared form is accurate to a
-        # relative 1e-6 of |A|^2; the stated 1e-5 relative target on the loss itself
-        # applies where the fit is not near-exact (no catastrophic cancellation).
+        # relative 3e-6 of |A|^2 (the tensor-core Gram products accumulate 64-K runs with
+        # truncation, a uniform -1.1e-6 relative bias on each of the two factors of pos);
+        # the stated 1e-5 relative target on the loss itself applies where the fit is
+        # not near-exact (no catastrophic cancellation).
         a2 = float((v.astype(np.float64) ** 2).sum())
-        assert abs(l * l - ls[-1] ** 2) < 1e-6 * a2
+        assert abs(l * l - ls[-1] ** 2) < 3e-6 * a2
         if ls[-1] ** 2 > 0.05 * a2:
             assert abs(l - ls[-1]) < 1e-5 * ls[-1]        # stated target
         assert np.all(np.isfinite(W)) and np.all(np.isfinite(H))
