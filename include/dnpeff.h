@@ -276,6 +276,32 @@ int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows
 int dnpeff_op_block_product(const float* X, int64_t M, int64_t K, const float* Y, int32_t r, float* C,
                             void* stream);
 
+/* Hoyer's sparseness projection of the components of W: every column of the
+ * row-major W[n, r] is replaced by the closest non-negative vector whose entries
+ * sum to l1_norm and whose Euclidean norm is l2_norm ("Non-negative Matrix
+ * Factorization with Sparseness Constraints", Hoyer 2004, projection operator).
+ * Replaces DenseFactorSparsityContext::sparsifyF
+ * (src/nmf/sparse/dense_factor_sparsity_constraints.h:205-237) and its kernels
+ * (src/nmf/sparse/sparsity_constraint_kernels.h:14-141), which the reference
+ * builds for W on device 0 from --sparsity_W (= l1_norm; l2_norm 1,
+ * mains/run_nmf_on_pefs.cu:200) but never calls (the call in MuNmf::run,
+ * multi_mu_dense_factors_nmf1.h:162, is commented out).
+ *   alpha_rule 0: alpha is the non-negative root of |m + alpha (s - m)| = l2_norm,
+ *     as published; the result has exactly the requested norms.
+ *   alpha_rule 1: the reference's kernel_computeAlpha expression, which is that root
+ *     only when m and s - m are parallel.
+ *   max_passes <= 0: n + 1 (a pass removes at least one entry of every column that
+ *     is still active); the reference loops without a limit.
+ *   passes / converged (may be NULL): passes made; 1 when no column is left active.
+ * The call synchronises the stream once per pass (as the reference's
+ * isFinishedSync) and allocates its scratch (9 bytes per element of W at most).
+ * dnpeff_sparsify_w applies it to the engine's W (every rank of a column-sharded
+ * run holds the same W and gets the same result). */
+int dnpeff_op_hoyer_project(float* W, int64_t n, int32_t r, float l1_norm, float l2_norm, int32_t alpha_rule,
+                            int32_t max_passes, int32_t* passes, int32_t* converged, void* stream);
+int dnpeff_sparsify_w(dnpeff_engine* eng, float l1_norm, float l2_norm, int32_t alpha_rule, int32_t* passes,
+                      int32_t* converged);
+
 /* Allocation-free variant of dnpeff_op_gram (no counterpart in the reference).
  *
  * For callers that must not allocate device memory at call time: code running

@@ -68,6 +68,8 @@ SIGNATURES = {
     "dnpeff_op_gram": (C.c_int, [_P, _I64, _I32, _P, _P]),
     "dnpeff_op_mu_update": (C.c_int, [_P, _P, _P, _I64, _I32, C.c_float, _P]),
     "dnpeff_op_block_product": (C.c_int, [_P, _I64, _I64, _P, _I32, _P, _P]),
+    "dnpeff_op_hoyer_project": (C.c_int, [_P, _I64, _I32, C.c_float, C.c_float, _I32, _I32, _P, _P, _P]),
+    "dnpeff_sparsify_w": (C.c_int, [_P, C.c_float, C.c_float, _I32, _P, _P]),
     "dnpeff_pef_hdf5_info": (C.c_int, [C.c_char_p] + [C.POINTER(_I64)] * 3),
     "dnpeff_read_pef_hdf5": (C.c_int, [C.c_char_p, _I64, _I64, _P, _P, _P]),
     "dnpeff_load_pef_hdf5": (C.c_int, [_P, C.c_char_p, _I64, _I64, _I32]),

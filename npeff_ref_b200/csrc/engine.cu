@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 #include "kernels_dense.cuh"
+#include "kernels_hoyer.cuh"
 #include "kernels_prep.cuh"
 #include "kernels_spmm.cuh"
 #include "kernels_tc.cuh"
@@ -1628,6 +1629,42 @@ int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows
     DN_TRY(op_err_word(&err));
     DN_TRY(mu_update_any(X, Num, G, rows, r, eps, scratch, err, (cudaStream_t)stream));
     return op_check_err(err, (cudaStream_t)stream);
+}
+
+// The projection with its own scratch (released on return; the call synchronises).
+static int hoyer_run(float* W, int64_t n, int32_t r, float l1, float l2, int32_t rule, int32_t max_passes,
+                     int32_t* passes, int32_t* converged, cudaStream_t st) {
+    if (n < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
+    if (!(l1 > 0.f) || !(l2 > 0.f)) return fail(DNPEFF_ERR_INVALID, "the L1 and L2 norms must be positive");
+    if (rule != 0 && rule != 1) return fail(DNPEFF_ERR_INVALID, "alpha_rule must be 0 or 1");
+    if (max_passes <= 0) max_passes = (int32_t)std::min<int64_t>(n + 1, INT32_MAX);  // a pass zeroes >= 1 entry per active column
+    int np = 0, conv = 1;
+    if (n > 0) {
+        HoyerPlan plan = hoyer_plan(n, r);
+        DevBuf<unsigned char> scratch;
+        DN_TRY(scratch.alloc(plan.bytes));
+        int* h_count = nullptr;
+        DN_CUDA(cudaHostAlloc((void**)&h_count, sizeof(int), cudaHostAllocDefault));
+        int s = hoyer_project(W, n, r, l1, l2, rule, max_passes, scratch.p, plan, h_count, &np, &conv, st);
+        cudaStreamSynchronize(st);
+        cudaFreeHost(h_count);
+        if (s != DNPEFF_OK) return s;
+    }
+    if (passes) *passes = np;
+    if (converged) *converged = conv;
+    return DNPEFF_OK;
+}
+
+int dnpeff_op_hoyer_project(float* W, int64_t n, int32_t r, float l1_norm, float l2_norm, int32_t alpha_rule,
+                            int32_t max_passes, int32_t* passes, int32_t* converged, void* stream) {
+    return hoyer_run(W, n, r, l1_norm, l2_norm, alpha_rule, max_passes, passes, converged, (cudaStream_t)stream);
+}
+
+int dnpeff_sparsify_w(dnpeff_engine* e, float l1_norm, float l2_norm, int32_t alpha_rule, int32_t* passes,
+                      int32_t* converged) {
+    DN_TRY(check_ready(e, true));
+    DeviceGuard g(e->device);
+    return hoyer_run(e->W, e->n, e->p.rank, l1_norm, l2_norm, alpha_rule, 0, passes, converged, e->st);
 }
 
 int dnpeff_op_block_product(const float* X, int64_t M, int64_t K, const float* Y, int32_t r, float* C,

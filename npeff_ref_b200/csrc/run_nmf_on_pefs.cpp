@@ -8,10 +8,14 @@
 // --nmf_n_components --nmf_max_iter (required); --n_examples --n_fisher_values
 // --min_values_per_parameter --sparsity_W --initial_H_path --initial_W_path.
 // Unknown flags are ignored, as in the reference (it never calls
-// VerifyNoUnreadFlags).  --sparsity_W is parsed and ignored: the Hoyer
-// projection it would enable is dead code there (nmf1.h:162).
+// VerifyNoUnreadFlags).  --sparsity_W alone changes nothing, as in the reference:
+// there it only builds the Hoyer projection context for W (l1 = the flag's value,
+// l2 = 1) and the one call that would use it, on the initial W before the first
+// step, is commented out (multi_mu_dense_factors_nmf1.h:162).
 // Extra, optional: --eps (1e-8) --seed (43190432042) --init_scale (1 = unscaled
-// uniform) --n_devices (all) --log_every (10) --shard_mode (cyclic|contiguous).
+// uniform) --n_devices (all) --log_every (10) --shard_mode (cyclic|contiguous)
+// --sparsify_initial_W (0; 1 makes that call: with --sparsity_W > 0 the columns of
+// the initial W are projected onto L1 = sparsity_W, L2 = 1 before the first step).
 #include <atomic>
 #include <condition_variable>
 #include <cstdio>
@@ -82,7 +86,7 @@ int main(int argc, char** argv) {
     g_argc = argc;
     g_argv = argv;
     std::string output_path, pef_path, init_h_path, init_w_path, shard_mode_s = "cyclic";
-    int n_components = 0, max_iters = 0, min_values = 1, n_devices_flag = 0, log_every = 10;
+    int n_components = 0, max_iters = 0, min_values = 1, n_devices_flag = 0, log_every = 10, sparsify_initial_w = 0;
     long long n_examples = -1, n_fisher_values = -1, seed = 43190432042ll;
     float sparsity_w = -1.f, eps = 1e-8f, init_scale = 0.f;
     flag_str("output_path", &output_path, true);
@@ -101,7 +105,7 @@ int main(int argc, char** argv) {
     flag_num("n_devices", &n_devices_flag, false);
     flag_num("log_every", &log_every, false);
     flag_str("shard_mode", &shard_mode_s, false);
-    (void)sparsity_w;
+    flag_num("sparsify_initial_W", &sparsify_initial_w, false);
     const int shard_mode = shard_mode_s == "contiguous" ? DNPEFF_SHARD_CONTIGUOUS : DNPEFF_SHARD_CYCLIC;
 
     int64_t n = 0, k = 0, dense = 0;
@@ -217,6 +221,18 @@ int main(int argc, char** argv) {
         if (dnpeff_init_factors(eng, W_init.empty() ? nullptr : W_init.data(), Hs.empty() ? nullptr : Hs.data())) {
             fail_here("initialising the factors");
             std::exit(1);
+        }
+        if (sparsify_initial_w && sparsity_w > 0.f) {
+            int32_t passes = 0, conv = 0;
+            if (dnpeff_sparsify_w(eng, sparsity_w, 1.0f, 0, &passes, &conv)) {
+                fail_here("projecting the initial W");
+                std::exit(1);
+            }
+            if (d == 0) {
+                printf("Projected the initial W onto L1 = %g, L2 = 1: %d passes%s.\n", (double)sparsity_w, (int)passes,
+                       conv ? "" : " (not converged)");
+                fflush(stdout);
+            }
         }
         if (d == 0) { printf("Running NMF.\n"); fflush(stdout); }
         if (dnpeff_run(eng, max_iters, log_every)) { fail_here("running the NMF"); fprintf(stderr, "%s\n", first_error.c_str()); std::exit(1); }

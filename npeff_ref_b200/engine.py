@@ -227,6 +227,15 @@ class MuNmf:
         check(lib().dnpeff_fit_w_only(self._h, int(iters), C.byref(v) if want_loss else None))
         return v.value if want_loss else None
 
+    def sparsify_w(self, l1_norm, l2_norm=1.0, alpha_rule=0):
+        """Hoyer's sparseness projection of every component (column) of W onto the given
+        L1 / L2 norms (``DenseFactorSparsityContext::sparsifyF``, built by the reference from
+        ``--sparsity_W`` but never called).  Returns (passes, converged)."""
+        passes, conv = C.c_int32(0), C.c_int32(0)
+        check(lib().dnpeff_sparsify_w(self._h, float(l1_norm), float(l2_norm), int(alpha_rule),
+                                      C.byref(passes), C.byref(conv)))
+        return passes.value, bool(conv.value)
+
     # -- measurement --------------------------------------------------------------
     def enable_timing(self, on=True):
         check(lib().dnpeff_enable_timing(self._h, 1 if on else 0))

@@ -281,6 +281,75 @@ def numpy_run(vals, colind, rowptr, m, W, H, iters, eps):
 
 
 # ---------------------------------------------------------------------------
+# Hoyer's sparseness projection of the columns of W (n x r), the reference's
+# DenseFactorSparsityContext::sparsifyF: the sequence of
+# src/nmf/sparse/dense_factor_sparsity_constraints.h:205-237 (set-up: Y = 1,
+# column sums, computeInitialS; then per pass: sums and dot products, alpha,
+# updateSAfterAlpha, active columns, updateYAndS, updateSLastStep) with the
+# elementwise rules of src/nmf/sparse/sparsity_constraint_kernels.h:14-141.
+# The reference never calls it (multi_mu_dense_factors_nmf1.h:162), so there is
+# no output of the reference to pin this against: the pins are the properties of
+# the published projection (Hoyer 2004, section 3.3) checked in tests/.
+# Column sums are taken in float64 and rounded to float32 (the reference: cuBLAS
+# fp32 sums); every elementwise operation is a single float32 operation, in the
+# order of the kernels.  rule 0: alpha = non-negative root of
+# |m + alpha (s - m)| = L2 (as published); rule 1: the reference's
+# kernel_computeAlpha expression.  Returns (S, passes, converged).
+def hoyer_project(W, l1, l2=1.0, rule=0, max_passes=None):
+    f = np.float32
+    S = np.array(W, dtype=f, copy=True)
+    n, r = S.shape
+    if n == 0 or r == 0:
+        return S, 0, True
+    l1, l2 = f(l1), f(l2)
+    Y = np.ones((n, r), dtype=bool)
+    active = np.ones(r, dtype=bool)
+    if max_passes is None or max_passes <= 0:
+        max_passes = n + 1
+
+    def colsum(M):
+        return M.astype(np.float64).sum(axis=0).astype(f)
+
+    S = S + (l1 - colsum(S)) / f(n)                               # kernel_computeInitialS
+    passes, converged = 0, False
+    for _ in range(max_passes):
+        yy = colsum(Y)
+        ss = (S.astype(np.float64) ** 2).sum(axis=0).astype(f)
+        sy = (S.astype(np.float64) * Y).sum(axis=0).astype(f)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            beta = l1 / yy
+            m2 = (beta * beta) * yy
+            ms = beta * sy
+            d2 = np.maximum(f(1e-9), (m2 + ss) - f(2.0) * ms)
+            if rule == 1:                                          # kernel_computeAlpha as written
+                alpha = ((l2 * np.sqrt(d2) + m2) - ms) / d2
+            else:
+                b = ms - m2
+                c = m2 - l2 * l2
+                disc = np.maximum(f(0.0), b * b - d2 * c)
+                alpha = (np.sqrt(disc) - b) / d2
+            alpha = np.where(yy > 0, alpha, f(0.0)).astype(f)
+            mid = np.where(yy > 0, l1 / yy, f(0.0)).astype(f)
+        M = np.where(Y, mid[None, :], f(0.0)).astype(f)           # kernel_updateSAfterAlpha
+        S_new = (M + alpha[None, :] * (S - M)).astype(f)
+        S = np.where(active[None, :], S_new, S)
+        neg = ((S < 0) & active[None, :]).sum(axis=0)
+        active = active & (neg > 0)
+        passes += 1
+        if not active.any():
+            converged = True
+            break
+        a = active[None, :]                                        # kernel_updateYAndS
+        Y = np.where(a & Y & (S < 0), False, Y)
+        S = np.where(a & ~Y, f(0.0), S).astype(f)
+        sum_s, sum_y = colsum(S), colsum(Y)                        # kernel_updateSLastStep
+        with np.errstate(divide="ignore", invalid="ignore"):
+            cshift = ((sum_s - l1) / sum_y).astype(f)
+        S = np.where(a & Y, S - cshift[None, :], S).astype(f)
+    return S, passes, converged
+
+
+# ---------------------------------------------------------------------------
 # Synthetic D-PEF generator for tests (numpy; small sizes).  Column popularity
 # Zipf(alpha), k distinct columns per row drawn without replacement
 # (exponential-race form of successive sampling), value = g^2 * row scale with

@@ -170,3 +170,33 @@ def test_fit_coeffs_cli_rejects_unknown_and_missing_flags(tmp_path):
                           "--n_row_splits_pefs=1", "--nmf_max_iter=1", "--bogus=1"],
                          capture_output=True, text=True, timeout=60)
     assert res.returncode != 0 and "Unrecognized flags." in res.stdout
+
+
+def test_cli_sparsity_flag_is_inert_unless_the_projection_is_asked_for(tmp_path):
+    """--sparsity_W alone leaves the output unchanged (the reference builds the Hoyer
+    context from it and never calls it, multi_mu_dense_factors_nmf1.h:162);
+    --sparsify_initial_W=1 makes the commented-out call: the initial W is projected onto
+    L1 = sparsity_W, L2 = 1 before the first step."""
+    n, m, k, r, iters = 100, 3000, 80, 8, 10
+    vals, idx, norms = make_problem(n, m, k, seed=71)
+    pef = str(tmp_path / "pef.h5")
+    _write_pef(pef, vals, idx, norms, m)
+    common = ["--per_example_fishers=" + pef, "--nmf_n_components=%d" % r, "--nmf_max_iter=%d" % iters]
+    outs = [str(tmp_path / ("o%d.h5" % i)) for i in range(3)]
+    _run(*common, "--output_path=" + outs[0])
+    _run(*common, "--output_path=" + outs[1], "--sparsity_W=4.0")
+    stdout = _run(*common, "--output_path=" + outs[2], "--sparsity_W=4.0", "--sparsify_initial_W=1")
+    Wa, Ha, _, _ = _read_decomp(outs[0])
+    Wb, Hb, _, _ = _read_decomp(outs[1])
+    Wc, Hc, kept, _ = _read_decomp(outs[2])
+    assert np.array_equal(Wa, Wb) and np.array_equal(Ha, Hb)
+    assert re.search(r"Projected the initial W onto L1 = 4, L2 = 1: \d+ passes\.", stdout)
+    # against the oracle: project the generated W0, then the same iterations
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m, 1)
+    mk = len(n2o)
+    W0, H0 = O.init_factors(n, mk, r, SEED, 1.0)
+    W0p, _, conv = O.hoyer_project(W0, 4.0, 1.0, rule=0)
+    assert conv
+    Wo, Ho = O.run(v, c, rp, mk, W0p, H0, iters, 1e-8)
+    assert rel_fro(Wc, Wo) < 1e-4 and rel_fro(Hc, Ho) < 1e-4
+    assert rel_fro(Wc, Wa) > 1e-2

@@ -505,3 +505,75 @@ def test_fit_w_only_with_sparse_h_matches_oracle(torch_cuda, r):
     Wo, lo = O.fit_w_only(v, c, rp, mk, W0, Hd, iters, eps)
     assert rel_fro(W, Wo) < 1e-4
     assert abs(loss - lo) < 1e-5 * lo
+
+
+# ---------------------------------------------------------------------------
+# Hoyer projection of W (DenseFactorSparsityContext::sparsifyF and its kernels).
+def _hoyer_check(got, want):
+    # Column sums are float64 on both sides but in a different order, so an entry within
+    # ~1e-8 of zero may fall on the other side of it: tolerate a few such entries.
+    flips = (got == 0) != (want == 0)
+    assert flips.sum() <= 3, int(flips.sum())
+    assert np.all(np.abs(got[flips]) < 1e-6) and np.all(np.abs(want[flips]) < 1e-6)
+    assert np.allclose(got, want, rtol=2e-5, atol=1e-6), np.abs(got - want).max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rule", [0, 1])
+@pytest.mark.parametrize("n,r,sparseness", [(1, 4, 0.5), (257, 5, 0.4), (500, 8, 0.7), (3000, 128, 0.8),
+                                            (20000, 32, 0.9), (64, 256, 0.6)])
+def test_op_hoyer_project_matches_oracle(torch_cuda, n, r, sparseness, rule):
+    import ctypes as C
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    rng = np.random.default_rng(n * 3 + r)
+    W = rng.random((n, r), dtype=np.float32)
+    l2 = 1.0
+    l1 = float(np.sqrt(n) - (np.sqrt(n) - 1.0) * sparseness) * l2
+    cap = 300
+    want, wp, wc = O.hoyer_project(W, l1, l2, rule=rule, max_passes=cap)
+    dW = _dev(torch, W)
+    passes, conv = C.c_int32(-1), C.c_int32(-1)
+    st = torch.cuda.current_stream().cuda_stream
+    check(lib().dnpeff_op_hoyer_project(dW.data_ptr(), n, r, l1, l2, rule, cap, C.byref(passes), C.byref(conv), st))
+    torch.cuda.synchronize()
+    got = dW.cpu().numpy()
+    assert passes.value == wp and bool(conv.value) == wc
+    _hoyer_check(got, want)
+    if rule == 0 and wc and n > 1:
+        # the operator's own guarantees, independent of the oracle
+        assert got.min() >= 0
+        assert np.allclose(got.astype(np.float64).sum(axis=0), l1, rtol=2e-5)
+        assert np.allclose(np.sqrt((got.astype(np.float64) ** 2).sum(axis=0)), l2, rtol=2e-5)
+
+
+@pytest.mark.gpu
+def test_op_hoyer_project_rejects_bad_arguments(torch_cuda):
+    from npeff_ref_b200._lib import lib
+    torch = torch_cuda
+    dW = torch.ones((4, 4), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib().dnpeff_op_hoyer_project(dW.data_ptr(), 4, 4, -1.0, 1.0, 0, 0, None, None, st) != 0
+    assert lib().dnpeff_op_hoyer_project(dW.data_ptr(), 4, 4, 1.0, 1.0, 7, 0, None, None, st) != 0
+    assert lib().dnpeff_op_hoyer_project(dW.data_ptr(), 0, 4, 1.0, 1.0, 0, 0, None, None, st) == 0  # empty: no-op
+
+
+@pytest.mark.gpu
+def test_engine_sparsify_w_matches_oracle(torch_cuda):
+    from npeff_ref_b200 import MuNmfParams
+    n, m, k, r = 300, 4000, 200, 16
+    vals, idx, norms = make_problem(n, m, k, seed=5)
+    with _engine(MuNmfParams(rank=r, eps=1e-12, seed=0, init_scale=1.0)) as eng:
+        eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+        eng.init_factors()
+        W0 = eng.load_w_to_host()
+        l1 = float(np.sqrt(n) - (np.sqrt(n) - 1.0) * 0.8)
+        passes, conv = eng.sparsify_w(l1, 1.0)
+        W1 = eng.load_w_to_host()
+        want, wp, wc = O.hoyer_project(W0, l1, 1.0, rule=0)
+        assert conv and wc and passes == wp
+        _hoyer_check(W1, want)
+        # the run goes on from the projected W
+        eng.step_h()
+        eng.step_w()
+        assert np.all(np.isfinite(eng.load_w_to_host()))

@@ -206,3 +206,67 @@ def test_dense_to_csr_thresholding():
     v, rp, c = O.dense_to_csr(A, 0.2)
     assert v.tolist() == pytest.approx([0.5, 0.2, 0.3, 0.3]) and rp.tolist() == [0, 2, 2, 4] and c.tolist() == [0, 2, 1, 2]
     assert rp.dtype == np.int64 and c.dtype == np.int32
+
+
+# ---------------------------------------------------------------------------
+# Hoyer projection (DenseFactorSparsityContext::sparsifyF).  The reference never runs
+# it, so the pins are the published operator's own properties and a plain
+# per-vector float64 restatement of the published algorithm.
+def _hoyer_vector_f64(x, l1, l2):
+    """Hoyer 2004, section 3.3, one vector, float64."""
+    x = np.asarray(x, dtype=np.float64)
+    n = x.size
+    s = x + (l1 - x.sum()) / n
+    z = np.zeros(n, dtype=bool)
+    for _ in range(n + 1):
+        m = np.where(z, 0.0, l1 / (n - z.sum()))
+        d = s - m
+        a, b, c = (d * d).sum(), (m * d).sum(), (m * m).sum() - l2 * l2
+        alpha = (-b + np.sqrt(max(0.0, b * b - a * c))) / max(a, 1e-30)
+        s = m + alpha * d
+        if (s >= 0).all():
+            return s
+        z |= s < 0
+        s[z] = 0.0
+        s[~z] -= (s.sum() - l1) / (n - z.sum())
+    return s
+
+
+@pytest.mark.parametrize("n,r,sparseness", [(50, 3, 0.3), (400, 8, 0.6), (1000, 5, 0.9), (64, 16, 0.75)])
+def test_hoyer_projection_properties(n, r, sparseness):
+    rng = np.random.default_rng(n + r)
+    W = rng.random((n, r), dtype=np.float32)
+    l2 = 1.0
+    l1 = (np.sqrt(n) - (np.sqrt(n) - 1.0) * sparseness) * l2
+    S, passes, conv = O.hoyer_project(W, l1, l2, rule=0)
+    assert conv and 1 <= passes <= n + 1
+    assert S.dtype == np.float32 and S.min() >= 0
+    assert np.allclose(S.astype(np.float64).sum(axis=0), l1, rtol=2e-5)
+    assert np.allclose(np.sqrt((S.astype(np.float64) ** 2).sum(axis=0)), l2, rtol=2e-5)
+    # the same answer as the published algorithm, vector by vector in float64
+    for t in range(r):
+        want = _hoyer_vector_f64(W[:, t], l1, l2)
+        assert np.allclose(S[:, t], want, rtol=1e-4, atol=2e-6)
+    # a projected vector is a fixed point
+    S2, p2, c2 = O.hoyer_project(S, l1, l2, rule=0)
+    assert c2 and np.allclose(S2, S, rtol=1e-4, atol=2e-6)
+
+
+def test_hoyer_reference_alpha_rule_keeps_l1_and_sign_only():
+    """The reference's kernel_computeAlpha expression (rule 1) is not the root of the
+    quadratic: the result is non-negative with the requested L1 norm, but its L2 norm is
+    not the requested one.  Recorded so that the difference between the two rules stays visible."""
+    rng = np.random.default_rng(3)
+    W = rng.random((500, 8), dtype=np.float32)
+    S, passes, conv = O.hoyer_project(W, 8.0, 1.0, rule=1, max_passes=200)
+    assert conv and S.min() >= 0
+    assert np.allclose(S.astype(np.float64).sum(axis=0), 8.0, rtol=2e-5)
+    assert np.all(np.sqrt((S.astype(np.float64) ** 2).sum(axis=0)) > 1.2)
+
+
+def test_hoyer_empty_and_degenerate():
+    S, p, c = O.hoyer_project(np.zeros((0, 4), np.float32), 2.0)
+    assert S.shape == (0, 4) and p == 0 and c
+    # one row: the only vector with that L1 norm
+    S, p, c = O.hoyer_project(np.array([[0.3, 0.9]], np.float32), 2.0, 1.0)
+    assert c and np.allclose(S, 2.0)
