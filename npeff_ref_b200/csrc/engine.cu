@@ -1670,7 +1670,7 @@ int dnpeff_sparsify_w(dnpeff_engine* e, float l1_norm, float l2_norm, int32_t al
 int dnpeff_op_block_product(const float* X, int64_t M, int64_t K, const float* Y, int32_t r, float* C,
                             void* stream) {
     if (M < 0 || K < 0 || r <= 0) return fail(DNPEFF_ERR_INVALID, "bad shape");
-    if (!block_tc_ok(r)) return fail(DNPEFF_ERR_UNSUPPORTED, "rank must be 32, 64, 96 or 128");
+    if (!block_tc_ok(r)) return fail(DNPEFF_ERR_UNSUPPORTED, "rank must be 32, 64, 96, 128, 256, 384 or 512");
     if (M == 0) return DNPEFF_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (K == 0) {

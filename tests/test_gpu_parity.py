@@ -225,7 +225,8 @@ def test_seeded_init_bit_exact(torch_cuda):
 
 
 @pytest.mark.parametrize("M,K,r", [(1, 1, 32), (127, 63, 64), (128, 64, 128), (129, 65, 96), (1000, 777, 128),
-                                   (20000, 300, 32), (5000, 4100, 128), (300, 9000, 64)])
+                                   (20000, 300, 32), (5000, 4100, 128), (300, 9000, 64),
+                                   (700, 1000, 256), (129, 300, 512), (2000, 640, 384)])
 def test_op_block_product_matches_float64(torch_cuda, M, K, r):
     """The tensor-core kernel of the dense popular block on its own: C = X Y against a
     float64 product, with the sparsity and value range of a popular block (a quarter
