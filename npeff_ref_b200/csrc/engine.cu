@@ -326,19 +326,22 @@ size_t gram_any_scratch(int64_t rows, int r) {
 // num_is_scratch: the caller does not need Num after the call (the wide-rank kernel
 // cannot update X in place and then writes its result over Num before copying it back).
 int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int r, float eps,
-                  float* tc_scratch, int* err, cudaStream_t st, bool num_is_scratch = false) {
+                  float* tc_scratch, int* err, cudaStream_t st, bool num_is_scratch = false,
+                  float* out_buf = nullptr) {
     if (tensor_cores_enabled() && mu_update_tc_ok(r))
         return mu_update_tc_launch(X, Num, G, rows, r, eps, tc_scratch, err, st);
     if (tensor_cores_enabled() && mu_update_wide_ok(r) && rows > 0) {
         DevBuf<float> tmp;
-        float* out = const_cast<float*>(Num);
-        if (!num_is_scratch) {
+        // the result goes to Num when the caller is done with it, else to the caller's
+        // spare buffer of rows * r floats, else to a temporary
+        float* out = num_is_scratch ? const_cast<float*>(Num) : out_buf;
+        if (!out) {
             DN_TRY(tmp.alloc((size_t)(rows * r)));
             out = tmp.p;
         }
         DN_TRY(mu_update_wide_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
         DN_CUDA(cudaMemcpyAsync(X, out, sizeof(float) * (size_t)(rows * r), cudaMemcpyDeviceToDevice, st));
-        if (!num_is_scratch) DN_CUDA(cudaStreamSynchronize(st));  // tmp is released on return
+        if (tmp.p) DN_CUDA(cudaStreamSynchronize(st));  // tmp is released on return
         return DNPEFF_OK;
     }
     return mu_update_launch(X, Num, G, rows, r, eps, st);
@@ -905,7 +908,9 @@ int step_w(dnpeff_engine* e) {
     const int r = e->p.rank;
     DN_TRY(compute_ah_hh(e));
     ScopedTimer t(e, 3);
-    return mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st);
+    // the buffer of W^T*A (ms x r) is idle during a W update
+    return mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
+                         e->ms >= e->n ? e->WA : nullptr);
 }
 
 int step_h(dnpeff_engine* e) {
@@ -1551,10 +1556,15 @@ int dnpeff_fit_w_only(dnpeff_engine* e, int32_t iters, double* loss) {
         return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init");
     const int r = e->p.rank;
     DN_TRY(compute_ah_hh(e));
+    // wide ranks write the updated W beside the old one: one spare n x r buffer for all iterations
+    DevBuf<float> spare;
+    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0) DN_TRY(spare.alloc((size_t)(e->n * r)));
     for (int it = 0; it < iters; it++) {
         ScopedTimer t(e, 3);
-        DN_TRY(mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st));
+        DN_TRY(mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
+                             spare.p));
     }
+    if (spare.p) DN_CUDA(cudaStreamSynchronize(e->st));  // released on return
     if (loss) DN_TRY(loss_from_current(e, false, loss));
     return DNPEFF_OK;
 }

@@ -479,7 +479,7 @@ def test_retain_columns_loader_bit_exact(torch_cuda):
             eng.set_csr_retain(n, m, vals, idx, np.array([5, m], np.int32), None, k, norms)
 
 
-@pytest.mark.parametrize("r", [16, 64])
+@pytest.mark.parametrize("r", [16, 64, 256])   # 256: configuration 4's rank (panelled update kernel)
 def test_fit_w_only_with_sparse_h_matches_oracle(torch_cuda, r):
     """The fit_coeffs_to_sparse_H numerics (src/nmf/sparse2/nmf_sparse_H.h:116-127,
     298-345): retained columns, H from CSR arrays, W-only updates with eps 1e-7."""
