@@ -271,7 +271,8 @@ int dnpeff_op_mu_update(float* X, const float* Num, const float* G, int64_t rows
                         float eps, void* stream);
 /* dnpeff_op_block_product: C[M,r] = X[M,K] * Y[K,r], all row-major and dense, on
  *   the tensor-core kernel that multiplies the dense popular block of A (ranks
- *   32, 64, 96, 128; fp32-equivalent 3xTF32).  It stands for the popular columns'
+ *   32, 64, 96, 128 in one go, 256, 384, 512 in panels of 128 columns;
+ *   fp32-equivalent 3xTF32; other ranks: DNPEFF_ERR_UNSUPPORTED).  It stands for the popular columns'
  *   share of the same two cusparseSpMM calls; exposed for kernel-level tests. */
 int dnpeff_op_block_product(const float* X, int64_t M, int64_t K, const float* Y, int32_t r, float* C,
                             void* stream);
