@@ -339,7 +339,11 @@ int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int 
             DN_TRY(tmp.alloc((size_t)(rows * r)));
             out = tmp.p;
         }
-        DN_TRY(mu_update_wide_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
+        static const bool no_pair = getenv("DNPEFF_WIDE_PAIR") && atoi(getenv("DNPEFF_WIDE_PAIR")) == 0;
+        if (mu_update_wide2_ok(r) && !no_pair)
+            DN_TRY(mu_update_wide2_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
+        else
+            DN_TRY(mu_update_wide_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
         DN_CUDA(cudaMemcpyAsync(X, out, sizeof(float) * (size_t)(rows * r), cudaMemcpyDeviceToDevice, st));
         if (tmp.p) DN_CUDA(cudaStreamSynchronize(st));  // tmp is released on return
         return DNPEFF_OK;
