@@ -1447,19 +1447,16 @@ int dnpeff_get_h(dnpeff_engine* e, float* out) {
     DeviceGuard g(e->device);
     const int r = e->p.rank;
     if (e->ms > 0) {
-        DevBuf<float> tmp, tmp2;
-        DN_TRY(tmp.alloc((size_t)(e->ms * r)));
+        DevBuf<float> tmp2;
         float* t = e->WA;  // free between iterations
         if (!t) {
             DN_TRY(tmp2.alloc((size_t)(e->ms * r)));
             t = tmp2.p;
         }
-        // local column j is internal row inv_perm[j]
-        k_gather_rows<<<kNumSMs * 8, 256, 0, e->st>>>(e->H, e->inv_perm, e->ms, r, tmp.p);
+        // local column j is internal row inv_perm[j]; gathered and transposed in one pass
+        k_gather_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(e->H, e->inv_perm, e->ms, r, t);
         DN_LAUNCH_CHECK();
-        k_transpose<<<kNumSMs * 8, dim3(32, 8), 0, e->st>>>(tmp.p, t, e->ms, r);
-        DN_LAUNCH_CHECK();
-        DN_COUNT_LAUNCH(2);
+        DN_COUNT_LAUNCH(1);
         DN_CUDA(cudaMemcpyAsync(out, t, sizeof(float) * (size_t)(e->ms * r), cudaMemcpyDeviceToHost, e->st));
         DN_TRY(check_kernel_status(e));
     }

@@ -634,4 +634,27 @@ __global__ void k_transpose(const float* __restrict__ in, float* __restrict__ ou
     }
 }
 
+// out[c, j] = in[index[j], c]: the rows of `in` ([*, cols] row-major) picked by `index`
+// (n_out of them) and transposed in one pass (the gather of the internal column order
+// fused with the device -> file layout transpose).
+__global__ void k_gather_transpose(const float* __restrict__ in, const int32_t* __restrict__ index, int64_t n_out,
+                                   int64_t cols, float* __restrict__ out) {
+    __shared__ float tile[32][33];
+    int64_t tiles_c = (cols + 31) / 32;
+    int64_t tiles_r = (n_out + 31) / 32;
+    for (int64_t t = blockIdx.x; t < tiles_c * tiles_r; t += gridDim.x) {
+        int64_t tr = t / tiles_c, tc = t % tiles_c;
+        for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+            int64_t j = tr * 32 + i, c_ = tc * 32 + threadIdx.x;
+            tile[i][threadIdx.x] = (j < n_out && c_ < cols) ? in[(int64_t)index[j] * cols + c_] : 0.f;
+        }
+        __syncthreads();
+        for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+            int64_t c_ = tc * 32 + i, j = tr * 32 + threadIdx.x;
+            if (c_ < cols && j < n_out) out[c_ * n_out + j] = tile[threadIdx.x][i];
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace dnpeff
