@@ -174,6 +174,12 @@ def run_reference_arm(args, c, cfg_id):
     if rank != 0:
         return
     from oracle import oracle as O
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks; this arm is rank 0 alone and is
+    # meant to use every host thread it may run on
+    try:
+        O.set_num_threads(len(os.sched_getaffinity(0)))
+    except Exception:
+        pass
     ns = args.cpu_sample_rows
     rng = np.random.default_rng(c["seed"])
     n, m, k = c["n"], c["m"], c["k"]
