@@ -118,103 +118,126 @@ def physical_gpu_index(local_rank):
 
 
 # ---------------------------------------------------------------------------
-def cpu_baseline(c, sample_rows, host_vals, host_idx, host_norms, col_div=1, threads=None):
-    """Times the CPU oracle on `sample_rows` rows of the workload and scales the
-    row-proportional parts to the full row count.  The feature-proportional dense
-    parts (H*H^T, (W^T W)*H + update) are timed on the first m/col_div features
-    and scaled by col_div.  Returns (iter/s, description, cores)."""
+CPU_MAX_NNZ = 700 * 1000 * 1000   # entries of the CPU arm's matrix (host memory: ~40 bytes per entry and rank-128 factor rows)
+
+
+def cpu_rows(c):
+    """Rows of the workload the CPU arm iterates on: all of them while the matrix
+    stays below CPU_MAX_NNZ stored entries, else the leading rows that fit."""
+    return int(min(c["n"], max(1, CPU_MAX_NNZ // c["k"])))
+
+
+def all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm is one process
+    and is meant to use every host thread it may run on."""
     from oracle import oracle as O
-    if threads:
-        O.set_num_threads(threads)
-    cores = O.num_threads()
-    n, m, k, r = c["n"], c["m"], c["k"], c["r"]
-    ns = sample_rows
-    rowptr = np.arange(ns + 1, dtype=np.int64) * k
-    v = O.normalize_rows(np.ascontiguousarray(host_vals[:ns]).ravel(), rowptr, host_norms[:ns])
-    col = np.ascontiguousarray(host_idx[:ns]).ravel()
-    W = O.init_uniform(0, ns * r, 1, 0, 0.01).reshape(ns, r)
-    Ht = O.init_uniform(0, m * r, 1, 1, 0.01).reshape(m, r)
-    mc = max(1, m // col_div)
-    t = {}
-
-    def timed(name, fn):
-        t0 = time.perf_counter()
-        out = fn()
-        t[name] = time.perf_counter() - t0
-        return out
-
-    AH = timed("spmm_ah", lambda: O.spmm(v, col, rowptr, Ht, acc64=False))
-    HH = timed("gram_h", lambda: O.gram(Ht[:mc], acc64=False))
-    W1 = timed("mu_w", lambda: O.mu_update(W, AH, HH, EPS, acc64=False))
-    cv, cr, cp = O.csr_to_csc(v, col, rowptr, m)
-    WA = timed("spmm_wa", lambda: O.spmm(cv, cr, cp, W1, acc64=False))
-    # A^T*W costs a fixed walk over all m features (zero + write r floats each)
-    # plus a per-entry part; timing it on a matrix with no entries gives the walk.
-    timed("spmm_wa", lambda: O.spmm(cv, cr, cp, W1, acc64=False))  # second run, warm
-    ep = np.zeros(m + 1, dtype=np.int64)
-    timed("spmm_wa_empty", lambda: O.spmm(cv[:1], cr[:1], ep, W1, acc64=False))
-    WW = timed("gram_w", lambda: O.gram(W1, acc64=False))
-    timed("mu_h", lambda: O.mu_update(Ht[:mc], WA[:mc], WW, EPS, acc64=False))
-    scale = n / float(ns)
-    fixed = min(t["spmm_wa_empty"], t["spmm_wa"])
-    per_row = (t["spmm_wa"] - fixed) / ns
-    it = ((t["spmm_ah"] + t["mu_w"] + t["gram_w"]) * scale + fixed + per_row * n
-          + (t["gram_h"] + t["mu_h"]) * (m / float(mc)))
-    desc = ("first %d of %d rows, 1 iteration, fp32-accumulate oracle; sparse and W-side times "
-            "scaled by %d/%d (A^T*W as fixed + per-row part); H-side dense parts timed on %d of %d features and scaled; "
-            "parts(s)=%s" % (ns, n, n, ns, mc, m, {a: round(b, 3) for a, b in t.items()}))
-    return 1.0 / it, desc, cores
-
-
-def run_reference_arm(args, c, cfg_id):
-    """`--impl reference`: the reference has no CPU implementation of this path
-    (its engine is cuSPARSE/cuBLAS); the timed CPU arm is the oracle port with
-    all host threads.  Data comes from the numpy generator (no GPU is touched)."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    from oracle import oracle as O
-    # torchrun exports OMP_NUM_THREADS=1 to its ranks; this arm is rank 0 alone and is
-    # meant to use every host thread it may run on
     try:
         O.set_num_threads(len(os.sched_getaffinity(0)))
     except Exception:
         pass
-    ns = args.cpu_sample_rows
-    rng = np.random.default_rng(c["seed"])
-    n, m, k = c["n"], c["m"], c["k"]
-    # Zipf(alpha) columns by inverse-CDF draws; repeats inside a row are replaced
-    # by fresh draws (successive sampling), values g^2 * lognormal sorted descending.
-    p = (np.arange(m, dtype=np.float64) + 1.0) ** (-c["alpha"])
-    cdf = np.cumsum(p)
-    idx = np.empty((ns, k), dtype=np.int32)
-    vals = np.empty((ns, k), dtype=np.float32)
-    for i in range(ns):
-        got = np.zeros(0, dtype=np.int64)
-        while len(got) < k:
-            draw = np.searchsorted(cdf, rng.random(4 * k) * cdf[-1])
-            got = np.unique(np.concatenate([got, draw]))
-        keep = rng.permutation(got)[:k]
-        idx[i] = keep
-        vals[i] = np.sort(rng.standard_normal(k) ** 2 * rng.lognormal(0.0, c["sigma"]))[::-1]
-    norms = np.sqrt((vals.astype(np.float64) ** 2).sum(1)).astype(np.float32)
-    results = []
-    for _ in range(max(args.warmup, 0) + max(args.steps, 1)):
-        results.append(cpu_baseline(c, ns, vals, idx, norms, col_div=8))
-    timed = results[max(args.warmup, 0):]
-    value = float(np.mean([x[0] for x in timed]))
-    desc, cores = timed[-1][1], timed[-1][2]
+    return O.num_threads()
+
+
+def cpu_arm(c, vals, idx, norms, warmup, steps):
+    """The CPU oracle (float-accumulating rendering, OpenMP over all host threads) on
+    `vals/idx/norms` ([ns, k] arrays: the workload's leading ns rows, every column):
+    normalise + prune + transpose once (untimed, like the GPU arm's resident load),
+    then `warmup` + `steps` full iterations, each timed.  Returns (seconds per timed
+    step as a list, description, cores, kept columns)."""
+    from oracle import oracle as O
+    cores = all_host_threads()
+    ns, k = vals.shape
+    t0 = time.perf_counter()
+    prob = O.Problem(ns, c["m"], k, c["r"], vals, idx, norms, min_count=1, eps=EPS, seed=c["seed"])
+    t_setup = time.perf_counter() - t0
+    times = []
+    for _ in range(max(warmup, 0) + max(steps, 1)):
+        t0 = time.perf_counter()
+        prob.step(acc64=False)
+        times.append(time.perf_counter() - t0)
+    timed = times[max(warmup, 0):]
+    loss = prob.loss()
+    m_kept = prob.m_kept
+    prob.close()
+    whole = ns == c["n"]
+    desc = ("%s %d of %d rows, every column (%d kept), the same generator stream as the GPU arm; fp32-accumulating "
+            "CPU oracle, %d OpenMP threads; %d warm-up + %d timed full iterations of %.2f s mean (setup %.0f s untimed); "
+            "loss after them %.6f" % ("all" if whole else "the leading", ns, c["n"], m_kept, cores, max(warmup, 0),
+                                      len(timed), float(np.mean(timed)), t_setup, loss))
+    return timed, desc, cores, m_kept
+
+
+def run_reference_arm(args, c, cfg_id):
+    """`--impl reference`: the reference has no CPU implementation of this path (its
+    engine is cuSPARSE/cuBLAS on a GPU); the timed CPU arm is the oracle port on all
+    host threads, on the workload's own matrix: the host twin of the device generator
+    draws the same column indices bit for bit.  Every step is one full iteration on
+    all rows and all columns (configurations whose matrix exceeds CPU_MAX_NNZ entries:
+    the leading rows that fit, rate scaled by the row ratio and marked extrapolated).
+    No GPU is touched."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    all_host_threads()
+    ns = cpu_rows(c)
+    t0 = time.perf_counter()
+    vals, idx, norms = O.synth_pef_hashed(ns, c["m"], c["k"], alpha=c["alpha"], sigma=c["sigma"], seed=c["seed"])
+    t_gen = time.perf_counter() - t0
+    timed, desc, cores, _ = cpu_arm(c, vals, idx, norms, args.warmup, args.steps)
+    sec = float(np.mean(timed))
+    extrapolated = ns != c["n"]
+    if extrapolated:
+        sec *= c["n"] / float(ns)
+        desc += "; EXTRAPOLATED to %d rows by the row ratio" % c["n"]
+    value = 1.0 / sec
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / value,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * sec,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": workload_name(cfg_id, c)},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "config": {"workload": workload_name(cfg_id, c), "generate_s": round(t_gen, 1)},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
+                         "extrapolated": extrapolated},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def ref_gpu_engine_ms_per_step(c, h_vals, h_idx, h_norms, iters=10):
+    """The unmodified reference engine (cuSPARSE / cuBLAS / cuRAND / NCCL, compiled from
+    the reference's own headers into oracle/_ref/ref_engine where that tree was
+    mounted) on the same matrix: returns (ms per step as the engine itself prints it
+    in its `step N: loss [ms/step]` line, None) or (None, reason)."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_engine")
+    if not os.path.exists(exe):
+        return None, "oracle/_ref/ref_engine is not built (the reference tree was not mounted at build time)"
+    n, k = h_vals.shape
+    if n * k >= 2 ** 31:
+        return None, "the reference engine stops at 2^31 stored entries per device (cublasSnrm2 guard)"
+    import re
+    import struct
+    import tempfile
+    tmp = "/dev/shm" if os.path.isdir("/dev/shm") else None
+    try:
+        with tempfile.TemporaryDirectory(dir=tmp) as td:
+            fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
+            with open(fin, "wb") as f:
+                f.write(struct.pack("<3q", n, c["m"], n * k))
+                (np.arange(n + 1, dtype=np.int64) * k).astype(np.int32).tofile(f)
+                h_idx.tofile(f)
+                (h_vals / (h_norms[:, None] + np.float32(1e-9))).astype(np.float32).tofile(f)
+            res = subprocess.run([exe, fin, fout, str(c["r"]), str(iters), repr(EPS), str(c["seed"]), "1", "timing"],
+                                 capture_output=True, text=True, timeout=600)
+        if res.returncode != 0:
+            return None, "ref_engine exited %d: %s" % (res.returncode, res.stderr[-300:].replace("\n", " "))
+        found = re.findall(r"step \d+: \S+ \[([0-9.eE+-]+) ms/step\]", res.stdout)
+        if not found:
+            return None, "ref_engine printed no step line"
+        return float(found[-1]), None
+    except Exception as ex:  # disk space, time-out
+        return None, "%s: %s" % (type(ex).__name__, str(ex)[:200])
 
 
 # ---------------------------------------------------------------------------
@@ -289,7 +312,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
-    ap.add_argument("--cpu-sample-rows", type=int, default=256)
+    ap.add_argument("--no-ref-gpu-engine", action="store_true",
+                    help="skip the run of the unmodified reference engine on the same GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--scale-rows", type=float, default=1.0,
@@ -427,6 +451,15 @@ def main():
                 "every stored entry gathers r floats on chip (shared memory or L2), so the SpMM is not "
                 "HBM-bound for r >= 64; traffic is scaled from a small-case capture",
     }
+    # the loss after exactly K iterations from the seeded initial factors: what the
+    # end-to-end run below must arrive at (untimed)
+    loss_k_resident = None
+    if not args.no_e2e:
+        eng.init_factors()
+        for _ in range(args.steps):
+            eng.step_w()
+            eng.step_h()
+        loss_k_resident = eng.compute_uncached_loss()
     eng.close()
 
     # ---- e2e: host buffers -> loader -> K iterations -> W,H back, through the C ABI
@@ -469,23 +502,44 @@ def main():
         e2e_ms = float(te.item())
         h2d = h_vals.numel() * 4 + h_idx.numel() * 4 + h_norms.numel() * 4
         d2h = W_out.numel() * 4 + H_out.numel() * 4
+        loss_k_e2e = eng2.compute_uncached_loss()
         e2e = {"value": args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps,
                "ms_total": e2e_ms,
                "host_ms": {"load": round(1e3 * (tw[1] - tw[0]), 1), "iterate": round(1e3 * (tw[2] - tw[1]), 1),
                            "read_back": round(1e3 * (tw[3] - tw[2]), 1)},
                "what": "dnpeff_set_csr from pinned host arrays (upload, normalise, prune, shard, CSC) "
-                       "+ init + K iterations + dnpeff_get_w/get_h into pinned host arrays"}
+                       "+ init + K iterations + dnpeff_get_w/get_h into pinned host arrays",
+               # the end-to-end run against the resident run after the same K iterations
+               # from the same seeded factors (the slab-pipelined loader against the device loader)
+               "self_check": {"loss_after_k_resident": loss_k_resident, "loss_after_k_e2e": loss_k_e2e,
+                              "rel_diff": abs(loss_k_e2e - loss_k_resident) / max(abs(loss_k_resident), 1e-300)}}
+        if e2e["self_check"]["rel_diff"] > 1e-6:
+            raise SystemExit("end-to-end run disagrees with the resident run: %r" % (e2e["self_check"],))
         eng2.close()
-        host_sample = (h_vals.numpy(), h_idx.numpy(), h_norms.numpy())
+        host_arrays = (h_vals.numpy(), h_idx.numpy(), h_norms.numpy())
     else:
-        ns = args.cpu_sample_rows
-        host_sample = (d_vals[:ns].cpu().numpy(), d_idx[:ns].cpu().numpy(), d_norms[:ns].cpu().numpy())
+        host_arrays = None
 
+    # ---- CPU baseline and the reference's own GPU engine, rank 0 of a 1-GPU run only
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, desc, cores = cpu_baseline(c, min(args.cpu_sample_rows, n), *host_sample)
-        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+    ref_gpu = None
+    if rank == 0 and world == 1 and (not args.no_cpu_baseline or not args.no_ref_gpu_engine):
+        if host_arrays is None:
+            host_arrays = (d_vals.cpu().numpy(), d_idx.cpu().numpy(), d_norms.cpu().numpy())
+            del d_vals, d_idx
+            torch.cuda.empty_cache()
+        if not args.no_ref_gpu_engine:
+            ms_ref, why = ref_gpu_engine_ms_per_step(c, *host_arrays)
+            ref_gpu = {"ms_per_step": ms_ref, "unavailable": why,
+                       "what": "the unmodified reference engine (cuSPARSE/cuBLAS, oracle/_ref/ref_engine) on the same "
+                               "matrix and GPU; its own `step N: loss [ms/step]` print after 10 iterations"}
+        if not args.no_cpu_baseline:
+            ns = cpu_rows(c)
+            timed, desc, cores, _ = cpu_arm(c, host_arrays[0][:ns], host_arrays[1][:ns], host_arrays[2][:ns], 0, 1)
+            sec = float(np.mean(timed)) * (n / float(ns))
+            cpu = {"value": 1.0 / sec, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc,
+                   "extrapolated": ns != n}
 
     if rank == 0:
         line = {
@@ -500,7 +554,7 @@ def main():
                        "setup_s": {"generate": round(t_gen, 2), "load_resident": round(t_load, 2)},
                        "loss_before_timed": loss_before, "loss_after_timed": loss_after},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks,
+            "clocks": clocks, "ref_gpu_engine": ref_gpu,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

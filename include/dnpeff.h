@@ -81,6 +81,26 @@ int dnpeff_device_count(int* count);
 int dnpeff_create(const dnpeff_params* params, int device, void* stream, dnpeff_engine** out);
 int dnpeff_destroy(dnpeff_engine* eng);
 
+/* Engine options: tuning values and test hooks (no reference counterpart; the
+ * reference has no tunables beyond MuNmfParams).  Set before the call they affect;
+ * value 0 restores the built-in default.
+ *   "loader_slabs"      dnpeff_set_csr uploads the values in this many row slabs on a
+ *                       second stream and processes each as it lands (1..8; default: 4
+ *                       from 64 Mi entries on, else 1)
+ *   "tail_block_bytes"  bytes of H covered by one column block of the unpopular
+ *                       columns, i.e. per gather launch (default 48 MiB)
+ *   "popular_divisor"   a column is popular from ceil(n_rows / d) entries on (d >= 2;
+ *                       default 16 with the dense tensor-core block, else 8)
+ *   "keep_canonical_csr" 1: keep the shard's CSR in input order after the loader has
+ *                       built its own layout (needed by dnpeff_export_shard_csr;
+ *                       costs 8 bytes per stored entry; default 0)
+ *   "wait_limit"        polls after which a wait between the roles of the
+ *                       warp-specialised tensor-core kernel gives up (default 2^24);
+ *                       the kernel then leaves cleanly and the next call that reads the
+ *                       engine's status returns DNPEFF_ERR_CUDA
+ * Unknown names fail with DNPEFF_ERR_INVALID. */
+int dnpeff_set_option(dnpeff_engine* eng, const char* name, int64_t value);
+
 /* ---- loader: normalize -> prune -> shard -> CSR + CSC on the device -------
  * Replaces PefSparseFishers::normalizeFishers_inPlace (src/io/pef_fisher_h5.h:38-52),
  * removeSmallestL0NormColumns_inPlace (src/util/sparse_util.h:79-159),
@@ -101,6 +121,24 @@ int dnpeff_set_csr_device(dnpeff_engine* eng, int64_t n_rows, int64_t n_cols_ful
                           int64_t k_per_row, const int64_t* d_rowptr, const float* d_vals,
                           const int32_t* d_colind, const float* d_norms,
                           int32_t min_values_per_parameter);
+
+/* The loader for a matrix that arrives in row slices, one per engine of a job: the
+ * multi-GPU form of moveAToDeviceAsync (…device_contexts1.h:180-194), where the
+ * reference uploads to every device only that device's column partition (made on the
+ * host by splitColumnWise, src/util/matrix_util.h:24-69).  Here engine i of G passes
+ * rows [row_begin, row_begin + n_rows) of the matrix -- the range dnpeff_row_slice
+ * gives for (n_rows_total, G, i) -- so every engine uploads 1/G of the entries; the
+ * per-column counts are summed over the engines (one integer allreduce), every
+ * engine derives the same pruning map, and each entry travels over NVLink to the
+ * engine that owns its column (grouped ncclSend / ncclRecv).  The resulting shard is
+ * the same, bit for bit, as the one dnpeff_set_csr builds from the whole matrix.
+ * Collective: every engine of the job must make the call, after dnpeff_comm_init.
+ * rowptr (or NULL with k_per_row), vals, colind and norms describe the slice only;
+ * rowptr starts at 0. */
+int dnpeff_row_slice(int64_t n_rows_total, int32_t n_engines, int32_t index, int64_t* row_begin, int64_t* n_rows);
+int dnpeff_set_csr_rows(dnpeff_engine* eng, int64_t n_rows_total, int64_t n_cols_full, int64_t k_per_row,
+                        int64_t row_begin, int64_t n_rows, const int64_t* rowptr, const float* vals,
+                        const int32_t* colind, const float* norms, int32_t min_values_per_parameter);
 
 /* The same loader with the kept columns given as a list of original column ids
  * instead of a count threshold: CsrMatrix::RetainColumns_InPlace
@@ -312,10 +350,17 @@ int dnpeff_sparsify_w(dnpeff_engine* eng, float l1_norm, float l2_norm, int32_t 
  * of the library image (every GPU that loads the library holds it until the
  * process exits) instead of an allocated buffer; the call makes no cudaMalloc,
  * cudaFree or other allocating call.  Inputs and outputs are the caller's, as
- * for dnpeff_op_gram, and the result is the same.
+ * for dnpeff_op_gram.  The partial sums always come from the CUDA-core kernel
+ * (fp32 FMA, slabs folded in double), whereas dnpeff_op_gram takes the tensor-core
+ * kernel at the ranks that one supports: the two results agree to about 3e-6 of
+ * the largest entry, not bit for bit.  A row count whose default slab split would
+ * not fit the array is cut into fewer, longer slabs.
  *   - rank above DNPEFF_NOALLOC_MAX_RANK fails with DNPEFF_ERR_UNSUPPORTED;
- *   - the first call on a device looks up the array's device address; make that
- *     first call before starting any stream capture on that device;
+ *   - the first call on a device looks up the array's device address; under
+ *     CUDA's lazy module loading that lookup may load the library's module onto
+ *     the device, which materialises the array and can synchronise the device --
+ *     the only point where this entry point can cause either.  Make that first
+ *     call at set-up time, before starting any stream capture on that device;
  *   - all calls on a device share the one array: calls that can overlap on the
  *     GPU (different streams, different threads) race and must be serialised by
  *     the caller.  Nothing in the array needs clearing between calls. */

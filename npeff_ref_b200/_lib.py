@@ -36,7 +36,10 @@ SIGNATURES = {
     "dnpeff_device_count": (C.c_int, [C.POINTER(C.c_int)]),
     "dnpeff_create": (C.c_int, [C.POINTER(Params), C.c_int, _P, C.POINTER(_P)]),
     "dnpeff_destroy": (C.c_int, [_P]),
+    "dnpeff_set_option": (C.c_int, [_P, C.c_char_p, _I64]),
     "dnpeff_set_csr": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
+    "dnpeff_row_slice": (C.c_int, [_I64, _I32, _I32, C.POINTER(_I64), C.POINTER(_I64)]),
+    "dnpeff_set_csr_rows": (C.c_int, [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_set_csr_device": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_set_csr_retain": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "dnpeff_get_shape": (C.c_int, [_P] + [C.POINTER(_I64)] * 5),

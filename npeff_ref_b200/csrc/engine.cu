@@ -162,9 +162,15 @@ struct dnpeff_engine {
     float* a_vals = nullptr;
     int32_t* a_col = nullptr;
     int64_t* a_rowptr = nullptr;
+    // CSC arrays.  With the popular block kept dense only the other columns are ever
+    // read from the CSC: the arrays then hold entries [c_base, nnz) of the full CSC
+    // (c_base = c_colptr[n_hot]) and are addressed through csc_vals()/csc_rows(),
+    // which shift the pointers so that the offsets in c_colptr apply unchanged.
     float* c_vals = nullptr;
     int32_t* c_row = nullptr;
     int64_t* c_colptr = nullptr;
+    int64_t c_base = 0;
+    float* w_spare = nullptr;  // n x r, wide ranks only: where a W update is written before it replaces W
     int32_t* new_to_og = nullptr;
 
     // Internal column order: [n_hot popular columns][the rest], each in local-id
@@ -215,18 +221,32 @@ struct dnpeff_engine {
     double t_ms[DNPEFF_N_TIMERS] = {0};
     int64_t t_n[DNPEFF_N_TIMERS] = {0};
     int64_t launches0 = 0;
+
+    // dnpeff_set_option values; 0 = the built-in default
+    int opt_loader_slabs = 0;
+    int64_t opt_tail_block_bytes = 0;
+    int opt_popular_divisor = 0;
+    uint32_t opt_wait_limit = kTiledSpinLimit;
+    bool opt_keep_csr = false;
 };
 
 namespace {
 
 int check_kernel_status(dnpeff_engine* e);
 
+// A pointer `base` elements before p (never dereferenced below p + base).
+template <typename T>
+T* shifted(T* p, int64_t base) {
+    return reinterpret_cast<T*>(reinterpret_cast<uintptr_t>(p) - (uintptr_t)base * sizeof(T));
+}
+float* csc_vals(const dnpeff_engine* e) { return shifted(e->c_vals, e->c_base); }
+int32_t* csc_rows(const dnpeff_engine* e) { return shifted(e->c_row, e->c_base); }
+
 constexpr int kRedBlocks = 4 * kNumSMs;
 constexpr int kMaxHotTiles = 1024;            // tiles of popular columns per row walk
-// Slice of H gathered per tail launch.  It has to stay L2-resident while all rows
-// sweep it; every further launch costs about 11 us.  Measured on the headline
-// workload (A*H^T product, ms): 12 MB 12.8, 24 MB 12.0, 32 MB 11.7, 48 MB 11.4,
-// 64 MB 11.7, 96 MB 14.2.
+// Slice of H gathered per tail launch.  It has to stay L2-resident (126 MB, shared
+// with the A*H^T accumulator and the streamed entries) while all rows sweep it, and
+// every further launch costs about 11 us: 48 MB is the measured optimum on B200.
 constexpr int64_t kTailBlockBytes = 48 << 20;
 constexpr int kMaxTailBlocks = 512;
 
@@ -301,17 +321,18 @@ struct PhaseTrace {
 
 // Popular columns hold at least ceil(n / div) entries.  With the dense tensor-core
 // block a column pays off from a few percent of density on; the sparse tiled
-// kernel needs longer columns.  DNPEFF_HOT_DIV overrides (experiments).
-int hot_divisor(bool dense) {
-    const char* s = getenv("DNPEFF_HOT_DIV");
-    if (s && atoi(s) >= 2) return atoi(s);
+// kernel needs longer columns.
+int hot_divisor(const dnpeff_engine* e, bool dense) {
+    if (e->opt_popular_divisor >= 2) return e->opt_popular_divisor;
     return dense ? 16 : 8;
 }
 
 // G = X^T X: tcgen05 kernel where the rank allows, CUDA-core kernel otherwise.
-int gram_any(const float* X, int64_t rows, int r, float* G, float* scratch, int* err, cudaStream_t st) {
-    if (tensor_cores_enabled() && gram_tc_ok(r)) return gram_blk_launch(X, rows, r, G, scratch, err, st);
-    if (tensor_cores_enabled() && gram_wide_ok(r) && rows > 0) return gram_wide_launch(X, rows, r, G, scratch, err, st);
+int gram_any(const float* X, int64_t rows, int r, float* G, float* scratch, int* err, cudaStream_t st,
+             uint32_t wait_limit = kTiledSpinLimit) {
+    if (tensor_cores_enabled() && gram_tc_ok(r)) return gram_blk_launch(X, rows, r, G, scratch, err, st, wait_limit);
+    if (tensor_cores_enabled() && gram_wide_ok(r) && rows > 0)
+        return gram_wide_launch(X, rows, r, G, scratch, err, st, wait_limit);
     return gram_launch(X, rows, r, G, scratch, st);
 }
 
@@ -339,8 +360,7 @@ int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int 
             DN_TRY(tmp.alloc((size_t)(rows * r)));
             out = tmp.p;
         }
-        static const bool no_pair = getenv("DNPEFF_WIDE_PAIR") && atoi(getenv("DNPEFF_WIDE_PAIR")) == 0;
-        if (mu_update_wide2_ok(r) && !no_pair)
+        if (mu_update_wide2_ok(r))
             DN_TRY(mu_update_wide2_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
         else
             DN_TRY(mu_update_wide_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
@@ -354,6 +374,8 @@ int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int 
 void free_matrix(dnpeff_engine* e) {
     dev_free(e->a_vals); dev_free(e->a_col); dev_free(e->a_rowptr);
     dev_free(e->c_vals); dev_free(e->c_row); dev_free(e->c_colptr);
+    e->c_base = 0;
+    dev_free(e->w_spare);
     dev_free(e->new_to_og);
     dev_free(e->perm); dev_free(e->inv_perm);
     dev_free(e->b_vals); dev_free(e->b_col); dev_free(e->tail_off);
@@ -407,19 +429,37 @@ void shard_range(int64_t total, int n_shards, int idx, int64_t* start, int64_t* 
 }
 
 // The values may arrive in slabs of rows (a host upload still in flight): rows
-// [row_end[s-1], row_end[s]) are valid once ready[s] has fired.  Everything that
-// needs the column ids only runs before the first wait.
+// [row_end[s-1], row_end[s]) are valid once ready[s] has fired (a null event: valid
+// already).  Everything that needs the column ids only runs before the first wait.
 struct LoadSlabs {
-    int count = 0;
-    int64_t row_end[8];
-    cudaEvent_t ready[8];
+    std::vector<int64_t> row_end;
+    std::vector<cudaEvent_t> ready;
+    int count() const { return (int)row_end.size(); }
 };
 
 // d_retained != nullptr: the kept columns are that list of original ids (device
 // pointer, n_retained of them) instead of the columns with >= min_count entries.
+// The rows every engine of a job holds when the matrix arrives in row slices
+// (dnpeff_set_csr_rows): equal-size contiguous ranges, the remainder spread over
+// the leading engines.
+void row_slice(int64_t n_total, int n_parts, int idx, int64_t* begin, int64_t* count) {
+    *begin = n_total * idx / n_parts;
+    *count = n_total * (idx + 1) / n_parts - *begin;
+}
+
+// Row slice of the input (dnpeff_set_csr_rows): the arrays hold rows
+// [row_begin, row_begin + n_in) of the matrix and every engine of the job is making
+// the same call on its own slice.  Column counts are summed over the engines, and
+// every entry travels to the engine that owns its column.
+struct RowSlice {
+    int64_t n_in;
+    int64_t row_begin;
+};
+
 int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const int64_t* d_rowptr,
                 const float* d_vals, const int32_t* d_col, const float* d_norms, int32_t min_count,
-                const int32_t* d_retained = nullptr, int64_t n_retained = 0, const LoadSlabs* slabs = nullptr) {
+                const int32_t* d_retained = nullptr, int64_t n_retained = 0, const LoadSlabs* slabs = nullptr,
+                const RowSlice* slice = nullptr) {
     if (n < 0 || m_full < 0 || (d_rowptr == nullptr && k < 0))
         return fail(DNPEFF_ERR_INVALID, "negative shape");
     if (n >= INT32_MAX || m_full >= INT32_MAX)
@@ -428,11 +468,12 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     free_matrix(e);
     PoolScope pool_scope(st);
     const int r = e->p.rank;
+    const int64_t n_in = slice ? slice->n_in : n;  // rows the input arrays hold
 
-    int64_t nnz_in = n * k;
+    int64_t nnz_in = n_in * k;
     if (d_rowptr) {
-        if (n > 0) {
-            DN_TRY(read_small(e, d_rowptr + n, sizeof(int64_t), &nnz_in));
+        if (n_in > 0) {
+            DN_TRY(read_small(e, d_rowptr + n_in, sizeof(int64_t), &nnz_in));
         } else {
             nnz_in = 0;
         }
@@ -454,6 +495,12 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         k_count_columns<<<(unsigned)blocks, 256, 0, st>>>(d_col, nnz_in, m_full, counts.p, err.p);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
+    }
+    if (slice) {
+        // the pruning decision needs the counts over all rows: one integer sum over the
+        // engines; a bad index seen by any of them fails the load on all of them
+        DN_NCCL(nccl_api().AllReduce(counts.p, counts.p, (size_t)m_full + 1, ncclInt32, ncclSum, e->comm, st));
+        DN_NCCL(nccl_api().AllReduce(err.p, err.p, 1, ncclInt32, ncclMax, e->comm, st));
     }
     DN_TRY(read_small(e, err.p, sizeof(int), &herr));
     if (herr) return data_error(herr);
@@ -512,7 +559,57 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     DevBuf<int32_t> row_count;
     DN_TRY(row_count.alloc_zero((size_t)n + 1, st));
     DN_CUDA(cudaMalloc((void**)&e->a_rowptr, sizeof(int64_t) * (size_t)(n + 1)));
-    if (n > 0) {
+    // Row slices: for every engine d of the job, the lengths of this slice's rows
+    // inside d's columns (rc_to[d], with offsets off_to[d] for the extraction); the
+    // lengths travel to d, which puts the slices of all engines one after the other.
+    const int G = slice ? e->comm_size : 1;
+    std::vector<ShardMap> map_of((size_t)G);
+    std::vector<DevBuf<int32_t>> rc_to((size_t)(slice ? G : 0));
+    std::vector<DevBuf<int64_t>> off_to((size_t)(slice ? G : 0));
+    std::vector<int64_t> send_count((size_t)G, 0), slice_begin((size_t)G + 1, 0);
+    if (slice) {
+        for (int d = 0; d < G; d++) {
+            if (e->p.shard_mode == DNPEFF_SHARD_CYCLIC) {
+                int64_t w = m_kept > d ? (m_kept - d + G - 1) / G : 0;
+                map_of[(size_t)d] = {d, w, (int32_t)G, (int32_t)d, 1};
+            } else {
+                int64_t b = 0, w = 0;
+                shard_range(m_kept, G, d, &b, &w);
+                map_of[(size_t)d] = {b, w, 1, 0, 0};
+            }
+            int64_t sb = 0, sc = 0;
+            row_slice(n, G, d, &sb, &sc);
+            slice_begin[(size_t)d] = sb;
+            DN_TRY(rc_to[(size_t)d].alloc_zero((size_t)n_in + 1, st));
+            DN_TRY(off_to[(size_t)d].alloc((size_t)n_in + 1));
+            if (n_in > 0) {
+                int64_t blocks = std::min<int64_t>(n_in, (int64_t)kNumSMs * 32);
+                k_row_counts<<<(unsigned)blocks, 256, 0, st>>>(d_col, d_rowptr, k, n_in, og_to_new.p, map_of[(size_t)d],
+                                                              rc_to[(size_t)d].p, err.p);
+                DN_LAUNCH_CHECK();
+                DN_COUNT_LAUNCH(1);
+            }
+            DN_TRY(scan_exclusive<int32_t>(rc_to[(size_t)d].p, off_to[(size_t)d].p, n_in + 1, st));
+            DN_TRY(read_small(e, off_to[(size_t)d].p + n_in, sizeof(int64_t), &send_count[(size_t)d]));
+        }
+        slice_begin[(size_t)G] = n;
+        if (slice->row_begin != slice_begin[(size_t)e->comm_rank] ||
+            n_in != slice_begin[(size_t)e->comm_rank + 1] - slice_begin[(size_t)e->comm_rank])
+            return fail(DNPEFF_ERR_INVALID, "row slice of engine %d must be rows [%lld, %lld)", e->comm_rank,
+                        (long long)slice_begin[(size_t)e->comm_rank], (long long)slice_begin[(size_t)e->comm_rank + 1]);
+        DN_NCCL(nccl_api().GroupStart());
+        for (int d = 0; d < G; d++) {
+            const int64_t cnt_d = slice_begin[(size_t)d + 1] - slice_begin[(size_t)d];
+            if (d == e->comm_rank) continue;
+            if (n_in > 0) DN_NCCL(nccl_api().Send(rc_to[(size_t)d].p, (size_t)n_in, ncclInt32, d, e->comm, st));
+            if (cnt_d > 0)
+                DN_NCCL(nccl_api().Recv(row_count.p + slice_begin[(size_t)d], (size_t)cnt_d, ncclInt32, d, e->comm, st));
+        }
+        DN_NCCL(nccl_api().GroupEnd());
+        if (n_in > 0)
+            DN_CUDA(cudaMemcpyAsync(row_count.p + slice->row_begin, rc_to[(size_t)e->comm_rank].p, sizeof(int32_t) * (size_t)n_in,
+                                    cudaMemcpyDeviceToDevice, st));
+    } else if (n > 0) {
         int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 32);
         k_row_counts<<<(unsigned)blocks, 256, 0, st>>>(d_col, d_rowptr, k, n, og_to_new.p, map,
                                                       row_count.p, err.p);
@@ -528,8 +625,13 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     trace.mark("row counts + scan");
     // 5. (the order-preserving extraction needs the values and comes further down,
     //    slab by slab; everything up to there needs the column ids only)
-    DN_CUDA(cudaMalloc((void**)&e->a_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
-    DN_CUDA(cudaMalloc((void**)&e->a_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
+    // The shard's CSR in input order is an intermediate: it is kept only on request
+    // (option keep_canonical_csr, for dnpeff_export_shard_csr); otherwise one slab
+    // of it at a time lives in a temporary on its way into the bucketed layout.
+    if (e->opt_keep_csr) {
+        DN_CUDA(cudaMalloc((void**)&e->a_vals, sizeof(float) * (size_t)std::max<int64_t>(nnz, 1)));
+        DN_CUDA(cudaMalloc((void**)&e->a_col, sizeof(int32_t) * (size_t)std::max<int64_t>(nnz, 1)));
+    }
     // 6. internal column order: popular columns first (they get the tiled,
     //    shared-memory kernels), then the rest; both parts in local-id order
     DevBuf<int32_t> cnt_s, hot_flags, cnt_p;
@@ -541,7 +643,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     const bool fast = spmm_fast_rank(r);
     bool dense = fast && tensor_cores_enabled() && block_tc_ok(r);
     int tile = fast ? spmm_tile_rows(r) : 128;
-    int32_t hot_thr = (int32_t)std::max<int64_t>(2, ceil_div(n, hot_divisor(dense)));
+    int32_t hot_thr = (int32_t)std::max<int64_t>(2, ceil_div(n, hot_divisor(e, dense)));
     if (!fast || n < 32) hot_thr = INT32_MAX;  // no hot part
     DN_TRY(hot_flags.alloc((size_t)ms + 1));
     DN_TRY(hot_pos.alloc((size_t)ms + 1));
@@ -604,10 +706,9 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     //     narrow enough for their slice of H to stay in L2 while it is gathered
     {
         int64_t tail_cols = ms - n_hot;
-        int64_t tail_bytes = kTailBlockBytes;
-        if (const char* tb = getenv("DNPEFF_TAIL_MB"))  // experiments: size of a tail block's slice of H
-            if (atoi(tb) >= 1) tail_bytes = (int64_t)atoi(tb) << 20;
-        int64_t block = std::max<int64_t>(4096, (tail_bytes / (4 * (int64_t)r)) / 32 * 32);
+        const int64_t tail_bytes = e->opt_tail_block_bytes > 0 ? e->opt_tail_block_bytes : kTailBlockBytes;
+        const int64_t min_block = e->opt_tail_block_bytes > 0 ? 32 : 4096;
+        int64_t block = std::max<int64_t>(min_block, (tail_bytes / (4 * (int64_t)r)) / 32 * 32);
         int64_t nb = ceil_div(std::max<int64_t>(tail_cols, 1), block);
         if (nb > kMaxTailBlocks) {
             block = ceil_div(ceil_div(tail_cols, kMaxTailBlocks), 32) * 32;
@@ -642,21 +743,110 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         trace.mark("index-only phases done");
         // slab by slab, as the values arrive: extraction with the row normalisation
         // applied, bucketing of the rows, the dense copy of the popular part
-        const int n_slabs = slabs ? slabs->count : 1;
+        // Row slices: every engine extracts, for each engine d, its slice's entries in
+        // d's columns (normalised, column ids local to d, input order) and sends them;
+        // what arrives from engine s lands at rows [slice_begin[s], slice_begin[s+1]) of
+        // this shard's CSR in input order, which is then complete and bucketed below.
+        DevBuf<float> canon_v;
+        DevBuf<int32_t> canon_c;
+        if (slice) {
+            if (slabs)
+                for (cudaEvent_t ev : slabs->ready)
+                    if (ev) DN_CUDA(cudaStreamWaitEvent(st, ev, 0));
+            slabs = nullptr;
+            if (!e->opt_keep_csr) {
+                DN_TRY(canon_v.alloc((size_t)std::max<int64_t>(nnz, 1)));
+                DN_TRY(canon_c.alloc((size_t)std::max<int64_t>(nnz, 1)));
+            }
+            float* const cv = e->opt_keep_csr ? e->a_vals : canon_v.p;
+            int32_t* const cc = e->opt_keep_csr ? e->a_col : canon_c.p;
+            std::vector<DevBuf<float>> sv((size_t)G);
+            std::vector<DevBuf<int32_t>> sc((size_t)G);
+            std::vector<int64_t> recv_off((size_t)G + 1, 0);
+            for (int d = 0; d <= G; d++)
+                DN_TRY(read_small(e, e->a_rowptr + slice_begin[(size_t)d], sizeof(int64_t), &recv_off[(size_t)d]));
+            for (int d = 0; d < G; d++) {
+                const bool self = d == e->comm_rank;
+                // this engine's own part goes straight to its place
+                float* ov = self ? cv + recv_off[(size_t)d] : nullptr;
+                int32_t* oc = self ? cc + recv_off[(size_t)d] : nullptr;
+                if (!self) {
+                    DN_TRY(sv[(size_t)d].alloc((size_t)std::max<int64_t>(send_count[(size_t)d], 1)));
+                    DN_TRY(sc[(size_t)d].alloc((size_t)std::max<int64_t>(send_count[(size_t)d], 1)));
+                    ov = sv[(size_t)d].p;
+                    oc = sc[(size_t)d].p;
+                } else if (send_count[(size_t)d] != recv_off[(size_t)d + 1] - recv_off[(size_t)d]) {
+                    return fail(DNPEFF_ERR_INVALID, "internal: row-slice bookkeeping out of step");
+                }
+                if (n_in > 0) {
+                    k_extract_shard<<<(unsigned)std::min<int64_t>(n_in, (int64_t)kNumSMs * 32), 256, 0, st>>>(
+                        d_vals, d_col, d_rowptr, k, 0, n_in, d_norms, og_to_new.p, map_of[(size_t)d], off_to[(size_t)d].p,
+                        ov, oc);
+                    DN_LAUNCH_CHECK();
+                    DN_COUNT_LAUNCH(1);
+                }
+            }
+            DN_NCCL(nccl_api().GroupStart());
+            for (int d = 0; d < G; d++) {
+                if (d == e->comm_rank) continue;
+                if (send_count[(size_t)d] > 0) {
+                    DN_NCCL(nccl_api().Send(sv[(size_t)d].p, (size_t)send_count[(size_t)d], ncclFloat, d, e->comm, st));
+                    DN_NCCL(nccl_api().Send(sc[(size_t)d].p, (size_t)send_count[(size_t)d], ncclInt32, d, e->comm, st));
+                }
+                const int64_t cnt = recv_off[(size_t)d + 1] - recv_off[(size_t)d];
+                if (cnt > 0) {
+                    DN_NCCL(nccl_api().Recv(cv + recv_off[(size_t)d], (size_t)cnt, ncclFloat, d, e->comm, st));
+                    DN_NCCL(nccl_api().Recv(cc + recv_off[(size_t)d], (size_t)cnt, ncclInt32, d, e->comm, st));
+                }
+            }
+            DN_NCCL(nccl_api().GroupEnd());
+            DN_CUDA(cudaStreamSynchronize(st));  // the send buffers are released here
+            trace.mark("row slices exchanged");
+        }
+        // Row slabs: the caller's (an upload in flight), or cuts of about 256 Mi input
+        // entries, which bound the temporary that holds a slab in input order.
+        LoadSlabs own;
+        if (!slabs) {
+            const int64_t S = std::min<int64_t>(std::max<int64_t>(ceil_div(slice ? nnz : nnz_in, (int64_t)256 << 20), 1), 64);
+            for (int64_t sl = 0; sl < S; sl++) {
+                own.row_end.push_back(sl + 1 == S ? n : n * (sl + 1) / S);
+                own.ready.push_back(nullptr);
+            }
+            slabs = &own;
+        }
+        const int n_slabs = slabs->count();
+        std::vector<int64_t> slab_off((size_t)n_slabs + 1, 0);  // a_rowptr at the slab boundaries
+        for (int sl = 0; sl < n_slabs && n > 0; sl++)
+            DN_TRY(read_small(e, e->a_rowptr + slabs->row_end[sl], sizeof(int64_t), &slab_off[(size_t)sl + 1]));
+        DevBuf<float> t_vals;
+        DevBuf<int32_t> t_col;
+        if (!e->opt_keep_csr && !slice && n > 0) {
+            int64_t longest = 1;
+            for (int sl = 0; sl < n_slabs; sl++) longest = std::max(longest, slab_off[(size_t)sl + 1] - slab_off[(size_t)sl]);
+            DN_TRY(t_vals.alloc((size_t)longest));
+            DN_TRY(t_col.alloc((size_t)longest));
+        }
         int64_t row0 = 0;
         for (int sl = 0; sl < n_slabs && n > 0; sl++) {
-            const int64_t row1 = slabs ? slabs->row_end[sl] : n;
-            if (slabs) DN_CUDA(cudaStreamWaitEvent(st, slabs->ready[sl], 0));
+            const int64_t row1 = slabs->row_end[sl];
+            if (slabs->ready[sl]) DN_CUDA(cudaStreamWaitEvent(st, slabs->ready[sl], 0));
             if (row1 <= row0) continue;
             const int64_t rows = row1 - row0;
-            k_extract_shard<<<(unsigned)std::min<int64_t>(rows, (int64_t)kNumSMs * 32), 256, 0, st>>>(
-                d_vals, d_col, d_rowptr, k, row0, row1, d_norms, og_to_new.p, map, e->a_rowptr, e->a_vals, e->a_col);
-            DN_LAUNCH_CHECK();
+            // the slab in input order: at its place in the kept CSR, or in the temporary
+            // (addressed through a_rowptr all the same: the pointers are shifted)
+            float* cv = e->opt_keep_csr ? e->a_vals : (slice ? canon_v.p : shifted(t_vals.p, slab_off[(size_t)sl]));
+            int32_t* cc = e->opt_keep_csr ? e->a_col : (slice ? canon_c.p : shifted(t_col.p, slab_off[(size_t)sl]));
+            if (!slice) {
+                k_extract_shard<<<(unsigned)std::min<int64_t>(rows, (int64_t)kNumSMs * 32), 256, 0, st>>>(
+                    d_vals, d_col, d_rowptr, k, row0, row1, d_norms, og_to_new.p, map, e->a_rowptr, cv, cc);
+                DN_LAUNCH_CHECK();
+                DN_COUNT_LAUNCH(1);
+            }
             size_t smem = sizeof(int) * 8 * (size_t)std::max(bm.n_buckets, 1);
             k_bucket_rows<<<(unsigned)std::min<int64_t>(rows, (int64_t)kNumSMs * 16), 256, smem, st>>>(
-                e->a_vals, e->a_col, e->a_rowptr, row0, row1, e->inv_perm, bm, e->b_vals, e->b_col, e->tail_off);
+                cv, cc, e->a_rowptr, row0, row1, e->inv_perm, bm, e->b_vals, e->b_col, e->tail_off);
             DN_LAUNCH_CHECK();
-            DN_COUNT_LAUNCH(2);
+            DN_COUNT_LAUNCH(1);
             if (dense) {
                 k_fill_blocks<<<(unsigned)std::min<int64_t>(ceil_div(rows, 8), (int64_t)kNumSMs * 16), 256, 0, st>>>(
                     e->b_vals, e->b_col, e->a_rowptr, e->tail_off, (int)(nb + 1), row0, row1, e->plan_x1.k_chunks,
@@ -666,6 +856,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             }
             row0 = row1;
         }
+        if (t_vals.p || canon_v.p) DN_CUDA(cudaStreamSynchronize(st));  // the temporaries are released at the end of this scope
         trace.mark("extract, bucket, dense fill");
         if (dense) {
             dim3 tgrid((unsigned)e->plan_x1.m_tiles, (unsigned)e->plan_x2.m_tiles);
@@ -689,7 +880,7 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
 
     trace.mark("tail block sizes");
     // 7. |A|^2 and sum(A) of the shard
-    k_sum_sumsq<<<kRedBlocks, 256, 0, st>>>(e->a_vals, nnz, e->red_partial);
+    k_sum_sumsq<<<kRedBlocks, 256, 0, st>>>(e->b_vals, nnz, e->red_partial);
     DN_LAUNCH_CHECK();
     k_fold<<<1, 256, 0, st>>>(e->red_partial, kRedBlocks, 2, e->red_out);
     DN_LAUNCH_CHECK();
@@ -733,11 +924,24 @@ int fill_csc(dnpeff_engine* e, int mode) {
     const size_t bitmap_bytes = 2 * (size_t)ceil_div(e->n, 32) * sizeof(uint32_t);
     PoolScope pool_scope(st);
     PhaseTrace trace(st);
-    DevBuf<float> tvals;
-    DevBuf<int32_t> trow, cursor, long_cols;
+    // the temporary copy covers the CSC entries of the columns being filled:
+    // offsets [t_base, t_end) of c_colptr
+    int64_t t_base = 0, t_end = e->nnz;
+    if (mode != 0) {
+        int64_t split = 0;
+        DN_TRY(read_small(e, e->c_colptr + e->n_hot, sizeof(int64_t), &split));
+        if (mode == 1) t_base = split; else t_end = split;
+    }
+    if (t_base < e->c_base) return fail(DNPEFF_ERR_INVALID, "internal: CSC arrays do not cover the requested columns");
+    DevBuf<float> tvals_buf;
+    DevBuf<int32_t> trow_buf, cursor, long_cols;
     DevBuf<int> err, n_long;
-    DN_TRY(tvals.alloc((size_t)e->nnz));
-    DN_TRY(trow.alloc((size_t)e->nnz));
+    DN_TRY(tvals_buf.alloc((size_t)std::max<int64_t>(t_end - t_base, 1)));
+    DN_TRY(trow_buf.alloc((size_t)std::max<int64_t>(t_end - t_base, 1)));
+    float* const tvals = shifted(tvals_buf.p, t_base);
+    int32_t* const trow = shifted(trow_buf.p, t_base);
+    float* const cvals = csc_vals(e);
+    int32_t* const crows = csc_rows(e);
     DN_TRY(cursor.alloc_zero((size_t)e->ms, st));
     DN_TRY(long_cols.alloc((size_t)(col_last - col_first)));
     DN_TRY(err.alloc_zero(1, st));
@@ -745,7 +949,7 @@ int fill_csc(dnpeff_engine* e, int mode) {
     trace.mark("  csc: scratch");
     for (int seg = seg_first; seg < seg_last; seg++) {
         k_csc_scatter<<<(unsigned)ceil_div(e->n, 8), 256, 0, st>>>(e->a_rowptr, e->b_col, e->b_vals, e->n, segs, seg,
-                                                                  e->c_colptr, cursor.p, tvals.p, trow.p);
+                                                                  e->c_colptr, cursor.p, tvals, trow);
         DN_COUNT_LAUNCH(1);
     }
     DN_LAUNCH_CHECK();
@@ -758,8 +962,8 @@ int fill_csc(dnpeff_engine* e, int mode) {
     DN_CUDA(cudaStreamSynchronize(st));
     {
         int64_t blocks = std::min<int64_t>(ceil_div(col_last - col_first, 8), (int64_t)kNumSMs * 32);
-        k_csc_order_short<<<(unsigned)blocks, 256, 0, st>>>(e->c_colptr, col_first, col_last, tvals.p, trow.p,
-                                                           e->c_vals, e->c_row, err.p);
+        k_csc_order_short<<<(unsigned)blocks, 256, 0, st>>>(e->c_colptr, col_first, col_last, tvals, trow,
+                                                           cvals, crows, err.p);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(2);
     }
@@ -768,8 +972,8 @@ int fill_csc(dnpeff_engine* e, int mode) {
             return fail(DNPEFF_ERR_UNSUPPORTED, "columns longer than 512 entries need n_rows <= 819200");
         DN_CUDA(cudaFuncSetAttribute(k_csc_order_long, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bitmap_bytes));
         int blocks = std::min(h_long, kNumSMs * 8);
-        k_csc_order_long<<<blocks, 256, bitmap_bytes, st>>>(e->c_colptr, long_cols.p, h_long, e->n, tvals.p, trow.p,
-                                                           e->c_vals, e->c_row, err.p);
+        k_csc_order_long<<<blocks, 256, bitmap_bytes, st>>>(e->c_colptr, long_cols.p, h_long, e->n, tvals, trow,
+                                                           cvals, crows, err.p);
         DN_LAUNCH_CHECK();
         DN_COUNT_LAUNCH(1);
     }
@@ -785,12 +989,23 @@ int fill_csc(dnpeff_engine* e, int mode) {
 // (`full`: the export call).
 int build_csc(dnpeff_engine* e, bool full = false) {
     PhaseTrace trace(e->st);
+    if (full && e->csc_ready && e->c_base > 0) {
+        // the arrays were sized for the unpopular columns only: start over at full size
+        DN_CUDA(cudaStreamSynchronize(e->st));
+        dev_free(e->c_vals);
+        dev_free(e->c_row);
+        e->c_base = 0;
+        e->csc_ready = e->csc_hot_ready = false;
+    }
     if (!e->csc_ready) {
         trace.mark("(before CSC build)");
-        DN_CUDA(cudaMalloc((void**)&e->c_vals, sizeof(float) * (size_t)std::max<int64_t>(e->nnz, 1)));
-        DN_CUDA(cudaMalloc((void**)&e->c_row, sizeof(int32_t) * (size_t)std::max<int64_t>(e->nnz, 1)));
-        trace.mark("  csc: arrays allocated");
         const bool tail_only = e->x2 != nullptr && !full;
+        int64_t base = 0;
+        if (tail_only) DN_TRY(read_small(e, e->c_colptr + e->n_hot, sizeof(int64_t), &base));
+        DN_CUDA(cudaMalloc((void**)&e->c_vals, sizeof(float) * (size_t)std::max<int64_t>(e->nnz - base, 1)));
+        DN_CUDA(cudaMalloc((void**)&e->c_row, sizeof(int32_t) * (size_t)std::max<int64_t>(e->nnz - base, 1)));
+        e->c_base = base;
+        trace.mark("  csc: arrays allocated");
         DN_TRY(fill_csc(e, tail_only ? 1 : 0));
         e->csc_ready = true;
         e->csc_hot_ready = !tail_only;
@@ -832,7 +1047,7 @@ int spmm_ah(dnpeff_engine* e, float* AH) {
     if (e->x1) {
         // popular block on the tensor cores: AH = A_pop * H_pop (H's first n_hot rows)
         DN_TRY(block_tc_launch(e->x1, e->plan_x1, e->H, e->n, e->n_hot, r, AH, e->blk_ysplit, e->blk_partial,
-                               e->d_err, e->st));
+                               e->d_err, e->st, e->opt_wait_limit));
         accumulate = 1;
     } else if (e->n_hot > 0) {
         SpmmCall c;
@@ -865,15 +1080,15 @@ int spmm_ah(dnpeff_engine* e, float* AH) {
 int spmm_wa(dnpeff_engine* e) {
     const int r = e->p.rank;
     if (!spmm_fast_rank(r))
-        return spmm_dispatch(e->c_vals, e->c_row, e->c_colptr, e->ms, e->W, r, e->WA, e->plan_csc, e->st);
+        return spmm_dispatch(csc_vals(e), csc_rows(e), e->c_colptr, e->ms, e->W, r, e->WA, e->plan_csc, e->st);
     if (e->x2) {
         // popular columns on the tensor cores: WA[0, n_hot) = A_pop^T * W
         DN_TRY(block_tc_launch(e->x2, e->plan_x2, e->W, e->n_hot, e->n, r, e->WA, e->blk_ysplit, e->blk_partial,
-                               e->d_err, e->st));
+                               e->d_err, e->st, e->opt_wait_limit));
     } else if (e->n_hot > 0) {
         SpmmCall c;
         c.kind = kSpmmTiled;
-        c.vals = e->c_vals; c.ind = e->c_row;
+        c.vals = csc_vals(e); c.ind = csc_rows(e);
         c.seg = {e->c_colptr, nullptr, 0, 0};
         c.rows = e->n_hot; c.D = e->W; c.r = r; c.out = e->WA;
         c.d_rows = e->n;
@@ -883,7 +1098,7 @@ int spmm_wa(dnpeff_engine* e) {
     if (e->ms > e->n_hot) {
         SpmmCall c;
         c.kind = kSpmmRows;
-        c.vals = e->c_vals; c.ind = e->c_row;
+        c.vals = csc_vals(e); c.ind = csc_rows(e);
         c.seg = {e->c_colptr, nullptr, 0, 0};
         c.row_first = e->n_hot; c.rows = e->ms - e->n_hot;
         c.D = e->W; c.r = r; c.out = e->WA; c.plan = &e->plan_csc;
@@ -902,7 +1117,7 @@ int compute_ah_hh(dnpeff_engine* e) {
     }
     {
         ScopedTimer t(e, 2);
-        DN_TRY(gram_any(e->H, e->ms, r, HH, e->gram_scratch, e->d_err, e->st));
+        DN_TRY(gram_any(e->H, e->ms, r, HH, e->gram_scratch, e->d_err, e->st, e->opt_wait_limit));
     }
     DN_TRY(allreduce_f32(e, e->AHG, (size_t)(e->n * r + (int64_t)r * r)));
     return DNPEFF_OK;
@@ -911,10 +1126,21 @@ int compute_ah_hh(dnpeff_engine* e) {
 int step_w(dnpeff_engine* e) {
     const int r = e->p.rank;
     DN_TRY(compute_ah_hh(e));
+    // Wide ranks write the updated W beside the old one.  The buffer of W^T*A (ms x r)
+    // is idle during a W update and serves when it exists and is large enough;
+    // otherwise the engine keeps a spare n x r buffer (allocated once).
+    float* spare = nullptr;
+    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0) {
+        if (e->WA && e->ms >= e->n) {
+            spare = e->WA;
+        } else {
+            if (!e->w_spare) DN_CUDA(cudaMalloc((void**)&e->w_spare, sizeof(float) * (size_t)(e->n * r)));
+            spare = e->w_spare;
+        }
+    }
     ScopedTimer t(e, 3);
-    // the buffer of W^T*A (ms x r) is idle during a W update
     return mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
-                         e->ms >= e->n ? e->WA : nullptr);
+                         spare);
 }
 
 int step_h(dnpeff_engine* e) {
@@ -927,7 +1153,7 @@ int step_h(dnpeff_engine* e) {
     }
     {
         ScopedTimer t(e, 2);
-        DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st));
+        DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st, e->opt_wait_limit));
     }
     ScopedTimer t(e, 3);
     return mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st, true);
@@ -959,7 +1185,7 @@ int loss_from_current(dnpeff_engine* e, bool recompute_ah, double* out) {
     const int r = e->p.rank;
     ScopedTimer t(e, 5);
     if (recompute_ah) DN_TRY(compute_ah_hh(e));
-    DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st));
+    DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st, e->opt_wait_limit));
     DN_TRY(device_dot(e, e->AHG, e->W, e->n * r, e->red_out + 0));
     DN_TRY(device_dot(e, e->WW, e->AHG + e->n * r, (int64_t)r * r, e->red_out + 1));
     double h[2];
@@ -996,6 +1222,12 @@ int check_kernel_status(dnpeff_engine* e) {
     int h = 0;
     DN_CUDA(cudaMemcpyAsync(&h, e->d_err, sizeof(int), cudaMemcpyDeviceToHost, e->st));
     DN_CUDA(cudaStreamSynchronize(e->st));
+    if (h) {
+        // reported once: the word is cleared so that the engine can be used again
+        // (after new factors are set; what the interrupted kernels wrote is invalid)
+        cudaMemsetAsync(e->d_err, 0, sizeof(int), e->st);
+        cudaStreamSynchronize(e->st);
+    }
     if (h & kErrTiledTimeout)
         return fail(DNPEFF_ERR_CUDA, "a bulk-copy wait in the tiled SpMM kernel ran out; results are invalid");
     if (h & kErrTcTimeout)
@@ -1145,6 +1377,27 @@ int dnpeff_destroy(dnpeff_engine* e) {
     return DNPEFF_OK;
 }
 
+int dnpeff_set_option(dnpeff_engine* e, const char* name, int64_t value) {
+    if (!e || !name) return fail(DNPEFF_ERR_INVALID, "null argument");
+    if (value < 0) return fail(DNPEFF_ERR_INVALID, "option values are non-negative");
+    if (!strcmp(name, "loader_slabs")) {
+        if (value > 8) return fail(DNPEFF_ERR_INVALID, "loader_slabs: at most 8");
+        e->opt_loader_slabs = (int)value;
+    } else if (!strcmp(name, "tail_block_bytes")) {
+        e->opt_tail_block_bytes = value;
+    } else if (!strcmp(name, "popular_divisor")) {
+        if (value == 1 || value > INT32_MAX) return fail(DNPEFF_ERR_INVALID, "popular_divisor: 0 or >= 2");
+        e->opt_popular_divisor = (int)value;
+    } else if (!strcmp(name, "keep_canonical_csr")) {
+        e->opt_keep_csr = value != 0;
+    } else if (!strcmp(name, "wait_limit")) {
+        e->opt_wait_limit = value == 0 || value > kTiledSpinLimit ? kTiledSpinLimit : (uint32_t)value;
+    } else {
+        return fail(DNPEFF_ERR_INVALID, "unknown option '%s'", name);
+    }
+    return DNPEFF_OK;
+}
+
 int dnpeff_set_csr_device(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
                           const int64_t* d_rowptr, const float* d_vals, const int32_t* d_colind,
                           const float* d_norms, int32_t min_values_per_parameter) {
@@ -1159,7 +1412,8 @@ int dnpeff_set_csr_device(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full,
 namespace {
 int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
                  const int64_t* rowptr, const float* vals, const int32_t* colind, const float* norms,
-                 int32_t min_values_per_parameter, const int32_t* retained, int64_t n_retained);
+                 int32_t min_values_per_parameter, const int32_t* retained, int64_t n_retained,
+                 int64_t n_rows_total = -1, int64_t row_begin = 0);
 }
 
 int dnpeff_set_csr(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
@@ -1167,6 +1421,31 @@ int dnpeff_set_csr(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_
                    const float* norms, int32_t min_values_per_parameter) {
     return set_csr_host(e, n_rows, n_cols_full, k_per_row, rowptr, vals, colind, norms,
                         min_values_per_parameter, nullptr, 0);
+}
+
+int dnpeff_row_slice(int64_t n_rows_total, int32_t n_engines, int32_t index, int64_t* row_begin, int64_t* n_rows) {
+    if (n_rows_total < 0 || n_engines <= 0 || index < 0 || index >= n_engines || !row_begin || !n_rows)
+        return fail(DNPEFF_ERR_INVALID, "bad argument");
+    row_slice(n_rows_total, n_engines, index, row_begin, n_rows);
+    return DNPEFF_OK;
+}
+
+int dnpeff_set_csr_rows(dnpeff_engine* e, int64_t n_rows_total, int64_t n_cols_full, int64_t k_per_row,
+                        int64_t row_begin, int64_t n_rows, const int64_t* rowptr, const float* vals,
+                        const int32_t* colind, const float* norms, int32_t min_values_per_parameter) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    if (n_rows_total < 0 || n_rows < 0 || row_begin < 0 || row_begin + n_rows > n_rows_total)
+        return fail(DNPEFF_ERR_INVALID, "row slice outside the matrix");
+    if (e->p.n_shards == 1) {
+        if (row_begin != 0 || n_rows != n_rows_total)
+            return fail(DNPEFF_ERR_INVALID, "a single engine takes the whole matrix");
+        return set_csr_host(e, n_rows, n_cols_full, k_per_row, rowptr, vals, colind, norms, min_values_per_parameter,
+                            nullptr, 0);
+    }
+    if (e->comm_size != e->p.n_shards)
+        return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init first");
+    return set_csr_host(e, n_rows, n_cols_full, k_per_row, rowptr, vals, colind, norms, min_values_per_parameter,
+                        nullptr, 0, n_rows_total, row_begin);
 }
 
 int dnpeff_set_csr_retain(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
@@ -1179,9 +1458,12 @@ int dnpeff_set_csr_retain(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full,
 }
 
 namespace {
+// n_rows_total >= 0: the arrays hold rows [row_begin, row_begin + n_rows) of a matrix of
+// n_rows_total rows and every engine of the job makes this call on its own slice.
 int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
                  const int64_t* rowptr, const float* vals, const int32_t* colind, const float* norms,
-                 int32_t min_values_per_parameter, const int32_t* retained, int64_t n_retained) {
+                 int32_t min_values_per_parameter, const int32_t* retained, int64_t n_retained,
+                 int64_t n_rows_total, int64_t row_begin) {
     if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
     if (n_rows < 0) return fail(DNPEFF_ERR_INVALID, "negative shape");
     DeviceGuard g(e->device);
@@ -1205,7 +1487,7 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
         LoadSlabs& sl;
         ~UploadGuard() {
             if (s) { cudaStreamSynchronize(s); cudaStreamDestroy(s); }
-            for (int i = 0; i < sl.count; i++) cudaEventDestroy(sl.ready[i]);
+            for (cudaEvent_t ev : sl.ready) cudaEventDestroy(ev);
         }
     } upload_guard{up, slabs};
     if (nnz > 0) {
@@ -1217,7 +1499,8 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
         DN_CUDA(cudaEventRecord(ids_issued, e->st));
         DN_CUDA(cudaStreamWaitEvent(up, ids_issued, 0));
         cudaEventDestroy(ids_issued);
-        const int n_slabs = nnz >= ((int64_t)64 << 20) ? 4 : 1;
+        int n_slabs = nnz >= ((int64_t)64 << 20) ? 4 : 1;
+        if (e->opt_loader_slabs > 0) n_slabs = std::min(e->opt_loader_slabs, 8);
         int64_t off0 = 0;
         for (int i = 0; i < n_slabs; i++) {
             const int64_t row1 = i + 1 == n_slabs ? n_rows : n_rows * (i + 1) / n_slabs;
@@ -1225,10 +1508,11 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
             if (off1 > off0)
                 DN_CUDA(cudaMemcpyAsync(dv.p + off0, vals + off0, sizeof(float) * (size_t)(off1 - off0),
                                         cudaMemcpyHostToDevice, up));
-            DN_CUDA(cudaEventCreateWithFlags(&slabs.ready[i], cudaEventDisableTiming));
-            slabs.count = i + 1;
-            slabs.row_end[i] = row1;
-            DN_CUDA(cudaEventRecord(slabs.ready[i], up));
+            cudaEvent_t ev = nullptr;
+            DN_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+            slabs.row_end.push_back(row1);
+            slabs.ready.push_back(ev);
+            DN_CUDA(cudaEventRecord(ev, up));
             off0 = off1;
         }
     }
@@ -1247,9 +1531,11 @@ int set_csr_host(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t 
         if (n_retained > 0)
             DN_CUDA(cudaMemcpyAsync(dret.p, retained, sizeof(int32_t) * (size_t)n_retained, cudaMemcpyHostToDevice, e->st));
     }
-    int s = load_device(e, n_rows, n_cols_full, k_per_row, rowptr ? dr.p : nullptr, dv.p, dc.p,
+    RowSlice slice = {n_rows, row_begin};
+    const bool sliced = n_rows_total >= 0;
+    int s = load_device(e, sliced ? n_rows_total : n_rows, n_cols_full, k_per_row, rowptr ? dr.p : nullptr, dv.p, dc.p,
                         norms ? dn.p : nullptr, min_values_per_parameter, retained ? dret.p : nullptr, n_retained,
-                        slabs.count > 0 ? &slabs : nullptr);
+                        slabs.count() > 0 ? &slabs : nullptr, sliced ? &slice : nullptr);
     if (s != DNPEFF_OK) free_matrix(e);
     cudaStreamSynchronize(e->st);
     return s;
@@ -1310,6 +1596,9 @@ int dnpeff_get_shard_columns(dnpeff_engine* e, int32_t* kept_ids, int32_t* origi
 int dnpeff_export_shard_csr(dnpeff_engine* e, int64_t* rowptr, int32_t* colind, float* vals) {
     DN_TRY(check_ready(e, false));
     DeviceGuard g(e->device);
+    if ((colind || vals) && e->nnz > 0 && !e->a_vals)
+        return fail(DNPEFF_ERR_INVALID,
+                    "the CSR in input order was not kept: set option keep_canonical_csr to 1 before loading");
     if (rowptr) DN_CUDA(cudaMemcpyAsync(rowptr, e->a_rowptr, sizeof(int64_t) * (size_t)(e->n + 1), cudaMemcpyDeviceToHost, e->st));
     if (colind && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(colind, e->a_col, sizeof(int32_t) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
     if (vals && e->nnz > 0) DN_CUDA(cudaMemcpyAsync(vals, e->a_vals, sizeof(float) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
@@ -1329,8 +1618,8 @@ int dnpeff_export_shard_csc(dnpeff_engine* e, int64_t* colptr, int32_t* rowind, 
     DN_CUDA(cudaMemcpyAsync(cp.data(), e->c_colptr, sizeof(int64_t) * (size_t)(e->ms + 1), cudaMemcpyDeviceToHost, e->st));
     if (e->ms > 0) DN_CUDA(cudaMemcpyAsync(perm.data(), e->inv_perm, sizeof(int32_t) * (size_t)e->ms, cudaMemcpyDeviceToHost, e->st));
     if (e->nnz > 0) {
-        DN_CUDA(cudaMemcpyAsync(ri.data(), e->c_row, sizeof(int32_t) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
-        DN_CUDA(cudaMemcpyAsync(va.data(), e->c_vals, sizeof(float) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+        DN_CUDA(cudaMemcpyAsync(ri.data(), csc_rows(e), sizeof(int32_t) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
+        DN_CUDA(cudaMemcpyAsync(va.data(), csc_vals(e), sizeof(float) * (size_t)e->nnz, cudaMemcpyDeviceToHost, e->st));
     }
     DN_CUDA(cudaStreamSynchronize(e->st));
     int64_t q = 0;
@@ -1557,15 +1846,14 @@ int dnpeff_fit_w_only(dnpeff_engine* e, int32_t iters, double* loss) {
         return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init");
     const int r = e->p.rank;
     DN_TRY(compute_ah_hh(e));
-    // wide ranks write the updated W beside the old one: one spare n x r buffer for all iterations
-    DevBuf<float> spare;
-    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0) DN_TRY(spare.alloc((size_t)(e->n * r)));
+    // wide ranks write the updated W beside the old one: the engine's spare n x r buffer
+    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0 && !e->w_spare)
+        DN_CUDA(cudaMalloc((void**)&e->w_spare, sizeof(float) * (size_t)(e->n * r)));
     for (int it = 0; it < iters; it++) {
         ScopedTimer t(e, 3);
         DN_TRY(mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
-                             spare.p));
+                             e->w_spare));
     }
-    if (spare.p) DN_CUDA(cudaStreamSynchronize(e->st));  // released on return
     if (loss) DN_TRY(loss_from_current(e, false, loss));
     return DNPEFF_OK;
 }

@@ -19,6 +19,8 @@ struct NcclApi {
                               cudaStream_t) = nullptr;
     ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int, ncclComm_t,
                               cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -47,6 +49,8 @@ inline int nccl_load() {
     DN_SYM(CommDestroy, "ncclCommDestroy")
     DN_SYM(AllReduce, "ncclAllReduce")
     DN_SYM(Broadcast, "ncclBroadcast")
+    DN_SYM(Send, "ncclSend")
+    DN_SYM(Recv, "ncclRecv")
     DN_SYM(GroupStart, "ncclGroupStart")
     DN_SYM(GroupEnd, "ncclGroupEnd")
     DN_SYM(GetErrorString, "ncclGetErrorString")

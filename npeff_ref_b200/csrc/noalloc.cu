@@ -9,7 +9,10 @@
 //
 // The array's name is only a host-side handle in host code; the address the
 // kernels need comes from cudaGetSymbolAddress, looked up once per device (with
-// that device current) on the first call made on it.
+// that device current) on the first call made on it.  Under CUDA's lazy module
+// loading that first lookup may be what loads this module onto the device: the
+// 16 MiB array is materialised then, and the load can synchronise the device.
+// Every later call on that device neither allocates nor synchronises.
 #include <mutex>
 
 #include "common.cuh"
@@ -37,9 +40,11 @@ int scratch_for_current_device(float** out) {
     if (!g_scratch_addr[dev]) {
         float* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
-        if (e != cudaSuccess || !p)
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();  // the failed lookup must not surface again in a later, unrelated call
             return fail(DNPEFF_ERR_CUDA, "cudaGetSymbolAddress(static scratch) on device %d: %s", dev,
                         cudaGetErrorString(e));
+        }
         g_scratch_addr[dev] = p;
     }
     *out = g_scratch_addr[dev];

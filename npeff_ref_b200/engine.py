@@ -66,6 +66,10 @@ class MuNmf:
     def __exit__(self, *exc):
         self.close()
 
+    def set_option(self, name, value):
+        """Tuning values and test hooks of the engine (``dnpeff_set_option``)."""
+        check(lib().dnpeff_set_option(self._h, name.encode(), int(value)))
+
     # -- loader ---------------------------------------------------------------
     def set_csr(self, n_rows, n_cols_full, vals, colind, rowptr=None, k_per_row=0, norms=None,
                 min_values_per_parameter=1):
@@ -79,6 +83,32 @@ class MuNmf:
         check(lib().dnpeff_set_csr(self._h, int(n_rows), int(n_cols_full), int(k_per_row),
                                    _ptr(rowptr), _ptr(vals), _ptr(colind), _ptr(norms),
                                    int(min_values_per_parameter)))
+
+    @staticmethod
+    def row_slice(n_rows_total, n_engines, index):
+        """(row_begin, n_rows) of the slice engine ``index`` of ``n_engines`` passes to
+        :meth:`set_csr_rows`."""
+        b, c = C.c_int64(0), C.c_int64(0)
+        check(lib().dnpeff_row_slice(int(n_rows_total), int(n_engines), int(index), C.byref(b), C.byref(c)))
+        return b.value, c.value
+
+    def set_csr_rows(self, n_rows_total, n_cols_full, row_begin, vals, colind, rowptr=None, k_per_row=0,
+                     norms=None, min_values_per_parameter=1):
+        """Collective loader: this engine passes only its row slice of the matrix
+        (``vals``/``colind``/``norms`` of rows ``[row_begin, row_begin + n_rows)``); every
+        engine of the job calls it after :meth:`init_comm`.  The reference uploads to each
+        device only that device's partition (…device_contexts1.h:180-194)."""
+        vals = np.ascontiguousarray(vals, dtype=np.float32)
+        n_rows = (len(rowptr) - 1) if rowptr is not None else (vals.size // max(int(k_per_row), 1))
+        vals = vals.reshape(-1)
+        colind = np.ascontiguousarray(colind, dtype=np.int32).reshape(-1)
+        if rowptr is not None:
+            rowptr = np.ascontiguousarray(rowptr, dtype=np.int64)
+        if norms is not None:
+            norms = np.ascontiguousarray(norms, dtype=np.float32)
+        check(lib().dnpeff_set_csr_rows(self._h, int(n_rows_total), int(n_cols_full), int(k_per_row),
+                                        int(row_begin), int(n_rows), _ptr(rowptr), _ptr(vals), _ptr(colind),
+                                        _ptr(norms), int(min_values_per_parameter)))
 
     def set_csr_retain(self, n_rows, n_cols_full, vals, colind, retained_cols, rowptr=None, k_per_row=0,
                        norms=None):

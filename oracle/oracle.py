@@ -41,6 +41,9 @@ def lib():
         _lib.oracle_prune_columns.restype = C.c_int64
         _lib.oracle_split_columns.restype = C.c_int64
         _lib.oracle_num_threads.restype = C.c_int
+        _lib.oracle_synth_pef.restype = C.c_int
+        _lib.oracle_problem_create.restype = C.c_void_p
+        _lib.oracle_problem_loss.restype = C.c_double
     return _lib
 
 
@@ -373,3 +376,49 @@ def synth_pef(n, m, k, alpha=1.1, sigma=1.0, seed=0):
         idx[i] = cols.astype(np.int32)
     norms = np.sqrt((vals.astype(np.float64) ** 2).sum(axis=1)).astype(np.float32)
     return vals, idx, norms
+
+
+def synth_pef_hashed(n, m, k, alpha=1.1, sigma=1.0, seed=0):
+    """The benchmark's synthetic D-PEF rows, generated on the host by the twin of the
+    device generator (``dnpeff_synth_pef_device``): the same column indices bit for
+    bit, values to a few ulp.  Returns (vals [n,k], idx [n,k], norms [n])."""
+    vals = np.empty((n, k), dtype=np.float32)
+    idx = np.empty((n, k), dtype=np.int32)
+    norms = np.empty(n, dtype=np.float32)
+    rc = lib().oracle_synth_pef(C.c_int64(n), C.c_int64(m), C.c_int64(k), C.c_double(alpha), C.c_double(sigma),
+                                C.c_uint64(seed), _p(vals, C.c_float), _p(idx, C.c_int32), _p(norms, C.c_float))
+    if rc != 0:
+        raise ValueError("bad synthetic shape")
+    return vals, idx, norms
+
+
+class Problem:
+    """A D-PEF matrix loaded once (normalise, prune, CSC, seeded initial factors with
+    the benchmark's Uniform * sqrt(mean(A)/r) scale when ``init_scale <= 0``), then
+    iterated one step per call: what the timed CPU arm of the benchmark runs."""
+
+    def __init__(self, n, m, k, r, vals, idx, norms, min_count=1, eps=1e-12, seed=0, init_scale=0.0):
+        vals, idx = _f32(vals), _i32(idx)
+        norms = None if norms is None else _f32(norms)
+        mk = C.c_int64(0)
+        self._h = lib().oracle_problem_create(
+            C.c_int64(n), C.c_int64(m), C.c_int64(k), C.c_int64(r), _p(vals, C.c_float), _p(idx, C.c_int32),
+            None if norms is None else _p(norms, C.c_float), C.c_int32(min_count), C.c_float(eps),
+            C.c_uint64(seed), C.c_float(init_scale), C.byref(mk))
+        if not self._h:
+            raise MemoryError("the CPU problem does not fit host memory")
+        self.m_kept = mk.value
+
+    def step(self, acc64=False):
+        lib().oracle_problem_step(C.c_void_p(self._h), C.c_int(int(acc64)))
+
+    def loss(self):
+        return float(lib().oracle_problem_loss(C.c_void_p(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().oracle_problem_free(C.c_void_p(self._h))
+            self._h = None
+
+    def __del__(self):
+        self.close()

@@ -17,7 +17,10 @@
 // instance run with max_iters = 0 yields the initial W and H, and a second one
 // with the same seed reproduces them before iterating.
 //
-// usage: ref_engine <in.bin> <out.bin> <rank> <iters> <eps> <seed> <min_count>
+// usage: ref_engine <in.bin> <out.bin> <rank> <iters> <eps> <seed> <min_count> [timing]
+// With the word `timing` as the last argument only the iterating instance runs and
+// nothing is written: the engine's own "step N: loss [ms/step]" lines on stdout
+// (multi_mu_dense_factors_nmf1.h:186-201) are the result.
 // in.bin : int64 n, m, nnz; int32 rowptr[n+1]; int32 colind[nnz]; float vals[nnz]
 // out.bin: int64 n, m_kept, nnz_kept, rank, n_devices;
 //          int32 new_to_og[m_kept]; int32 rowptr[n+1]; int32 colind[nnz_kept]; float vals[nnz_kept];
@@ -49,6 +52,7 @@ int main(int argc, char** argv) {
     float eps = (float)atof(argv[5]);
     long seed = atol(argv[6]);
     int min_count = atoi(argv[7]);
+    const bool timing_only = argc >= 9 && strcmp(argv[8], "timing") == 0;
 
     FILE* f = fopen(argv[1], "rb");
     if (!f) { perror("open in"); return 1; }
@@ -73,6 +77,14 @@ int main(int argc, char** argv) {
     p.rank = rank;
     p.eps = eps;
     p.seed = seed;
+
+    if (timing_only) {
+        p.max_iters = iters;
+        MuNmf<int32_t> nmf(parts, p);
+        nmf.run();
+        fflush(stdout);
+        return 0;
+    }
 
     p.max_iters = 0;
     MuNmf<int32_t> nmf0(parts, p);

@@ -30,9 +30,14 @@ def _dev(torch, a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def _engine(params, **kw):
+def _engine(params, keep_csr=False, **kw):
+    """An engine; `keep_csr` keeps the shard's CSR in input order for export_shard_csr
+    (the loader drops that intermediate by default)."""
     from npeff_ref_b200 import MuNmf
-    return MuNmf(params, **kw)
+    eng = MuNmf(params, **kw)
+    if keep_csr:
+        eng.set_option("keep_canonical_csr", 1)
+    return eng
 
 
 def _csr_random(rng, rows, cols, lens):
@@ -130,7 +135,7 @@ def test_loader_bit_exact(torch_cuda, min_count, n_shards):
     v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m, min_count)
     mk = len(n2o)
     for s in range(n_shards):
-        with _engine(MuNmfParams(rank=8), shard_index=s, n_shards=n_shards) as eng:
+        with _engine(MuNmfParams(rank=8), keep_csr=True, shard_index=s, n_shards=n_shards) as eng:
             eng.set_csr(n, m, vals, idx, None, k, norms, min_count)
             nn, mkept, c0, ms, nnz = eng.shape
             assert (nn, mkept) == (n, mk)
@@ -160,7 +165,7 @@ def test_loader_cyclic_sharding_bit_exact(torch_cuda):
     rows = np.repeat(np.arange(n), np.diff(rp))
     seen = np.zeros(mk, dtype=bool)
     for d in range(G):
-        with _engine(MuNmfParams(rank=8, seed=4, init_scale=0.5), shard_index=d, n_shards=G,
+        with _engine(MuNmfParams(rank=8, seed=4, init_scale=0.5), keep_csr=True, shard_index=d, n_shards=G,
                      shard_mode=MuNmf.CYCLIC) as eng:
             eng.set_csr(n, m, vals, idx, None, k, norms, 2)
             kept_ids, og_ids = eng.shard_columns()
@@ -185,7 +190,7 @@ def test_loader_ragged_rows_and_empty_rows(torch_cuda):
     lens[[0, 7, 129]] = 0
     vals, ind, ptr = _csr_random(rng, n, m, lens)
     v, c, rp, n2o = O.prune_columns(vals, ind, ptr, m, 2)
-    with _engine(MuNmfParams(rank=4)) as eng:
+    with _engine(MuNmfParams(rank=4), keep_csr=True) as eng:
         eng.set_csr(n, m, vals, ind, ptr, 0, None, 2)
         assert np.array_equal(eng.new_to_og(), n2o)
         gv, gc, grp = eng.export_shard_csr()
@@ -440,7 +445,7 @@ def test_engine_matches_reference_engine_fixture(torch_cuda, path):
     from npeff_ref_b200 import MuNmfParams
     g = np.load(path)
     n, m, k, r = int(g["n"]), int(g["m"]), int(g["k"]), int(g["rank"])
-    with _engine(MuNmfParams(rank=r, eps=float(g["eps"]))) as eng:
+    with _engine(MuNmfParams(rank=r, eps=float(g["eps"])), keep_csr=True) as eng:
         eng.set_csr(n, m, g["in_vals"], g["in_col"], None, k, None, int(g["min_count"]))
         assert np.array_equal(eng.new_to_og(), g["new_to_og"])
         gv, gc, grp = eng.export_shard_csr()
@@ -452,6 +457,49 @@ def test_engine_matches_reference_engine_fixture(torch_cuda, path):
         assert rel_fro(eng.load_h_to_host(), g["H"]) < 1e-4
         l = eng.compute_uncached_loss()
         assert abs(l - float(g["loss"])) < 1e-3 * l   # the reference sums its loss terms in fp32
+
+
+_REF_WIDE = sorted(glob.glob(os.path.join(GOLDEN, "ref_wide_*.npz")))
+
+
+@pytest.mark.skipif(not _REF_WIDE, reason="no wide reference-engine fixtures recorded yet")
+@pytest.mark.parametrize("path", _REF_WIDE, ids=[os.path.basename(p) for p in _REF_WIDE])
+def test_engine_matches_reference_engine_wide_fixture(torch_cuda, path):
+    """Ranks 128 and 256 against the unmodified reference engine (cuSPARSE / cuBLAS) on
+    matrices whose popular block spans several row tiles and K splits, with several
+    tail column blocks: the fixture holds seeds (input: oracle.synth_pef; initial
+    factors: the engine's cuRAND calls repeated here), W, a sample of H's columns and
+    the norm of every column of H."""
+    import zlib
+    from npeff_ref_b200 import MuNmfParams
+    from helpers import curand_xorwow_uniform
+    g = np.load(path)
+    n, m, k, r = int(g["n"]), int(g["m"]), int(g["k"]), int(g["rank"])
+    vals, idx, norms = make_problem(n, m, k, seed=int(g["synth_seed"]))
+    assert [zlib.crc32(vals.tobytes()), zlib.crc32(idx.tobytes())] == list(g["in_crc"]), \
+        "the numpy generator no longer reproduces the fixture's input"
+    rowptr = np.arange(n + 1, dtype=np.int64) * k
+    v = O.normalize_rows(vals.ravel(), rowptr, norms)       # the harness was fed normalised values
+    with _engine(MuNmfParams(rank=r, eps=float(g["eps"])), keep_csr=True) as eng:
+        eng.set_option("tail_block_bytes", 4 << 20)
+        eng.set_csr(n, m, v, idx, None, k, None, int(g["min_count"]))
+        mk = eng.shape[1]
+        assert mk == int(g["m_kept"]) and np.array_equal(eng.new_to_og(), g["new_to_og"])
+        gv, gc, grp = eng.export_shard_csr()
+        assert zlib.crc32(gc.tobytes()) == int(g["p_col_crc"]) and zlib.crc32(gv.tobytes()) == int(g["p_vals_crc"])
+        n_pop, _, n_blocks, tile_rows = eng.layout()
+        assert n_pop > 256 and tile_rows == 0 and n_blocks >= 2
+        w0, h0 = curand_xorwow_uniform(int(g["seed"]), [n * r, r * mk])
+        assert np.array_equal(w0[:4096], g["W0_head"]) and np.array_equal(h0[:4096], g["H0_head"])
+        eng.init_factors(w0.reshape(r, n).T, h0.reshape(mk, r).T)   # the reference's matrices are column-major
+        eng.run(int(g["iters"]), log_every=0)
+        W, H = eng.load_w_to_host(), eng.load_h_to_host()
+        l = eng.compute_uncached_loss()
+    assert rel_fro(W, g["W"]) < 1e-4, rel_fro(W, g["W"])
+    assert rel_fro(H[:, g["H_cols"]], g["H_sample"]) < 1e-4
+    hn = np.sqrt((H.astype(np.float64) ** 2).sum(axis=0))
+    assert rel_fro(hn, g["H_col_norms"]) < 1e-4
+    assert abs(l - float(g["loss"])) < 1e-3 * l   # the reference sums its loss terms in fp32
 
 
 def test_retain_columns_loader_bit_exact(torch_cuda):
@@ -468,7 +516,7 @@ def test_retain_columns_loader_bit_exact(torch_cuda):
                                                np.setdiff1d(np.arange(m), used)[:20]])).astype(np.int32)
     retained = np.concatenate([retained, retained[:3]])        # three ids listed twice
     ev, ec, erp = O.retain_columns(nv, idx.ravel(), rowptr, m, retained)
-    with _engine(MuNmfParams(rank=8)) as eng:
+    with _engine(MuNmfParams(rank=8), keep_csr=True) as eng:
         eng.set_csr_retain(n, m, vals, idx, retained, None, k, norms)
         assert eng.shape[1] == len(retained)
         assert np.array_equal(eng.new_to_og(), retained)

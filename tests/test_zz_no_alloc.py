@@ -36,6 +36,30 @@ def test_gram_noalloc_matches_gram_twice_in_a_row():
         assert np.abs(g - ref.T @ ref).max() <= 3e-6 * np.abs(w).max()
 
 
+@pytest.mark.parametrize("rows,r", [(200000, 128), (10000, 1024)])
+def test_gram_noalloc_longer_slabs_when_the_default_split_does_not_fit(rows, r):
+    """From about 131 000 rows at rank 128, or 8 000 rows at rank 1024, the slab split
+    dnpeff_op_gram would use needs more than the fixed 16 MiB: the entry point then
+    cuts the rows into fewer, longer slabs.  Same comparison as above, twice in a row."""
+    import torch
+    from npeff_ref_b200._lib import lib, check
+    torch.cuda.set_device(0)
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device="cuda").manual_seed(rows + r)
+    X = torch.rand((rows, r), generator=g, device="cuda")
+    ref = (X.double().T @ X.double()).cpu().numpy()
+    want = torch.full((r, r), float("nan"), device="cuda")
+    check(lib().dnpeff_op_gram(X.data_ptr(), rows, r, want.data_ptr(), st))
+    for _ in range(2):
+        got = torch.full((r, r), float("nan"), device="cuda")
+        check(lib().dnpeff_op_gram_noalloc(X.data_ptr(), rows, r, got.data_ptr(), st))
+        torch.cuda.synchronize()
+        gnp = got.cpu().numpy()
+        assert np.abs(gnp - want.cpu().numpy()).max() <= 3e-6 * np.abs(ref).max()
+        assert np.abs(gnp - ref).max() <= 3e-6 * np.abs(ref).max()
+        assert np.array_equal(gnp, gnp.T)
+
+
 def test_gram_noalloc_rejects_rank_beyond_limit():
     import torch
     from npeff_ref_b200._lib import lib
