@@ -387,10 +387,28 @@ def main():
             dist.all_reduce(s)
         return math.sqrt(float(s.item()) / (n * eng.shape[1]) / r)
 
+    # The rows this rank will hand to the end-to-end loader (and rank 0 to the CPU arm)
+    # go to pinned host memory now, so that the generator's device arrays can be
+    # released as soon as the resident engine has loaded them (at configuration 3 they
+    # are 26 GB beside a 130 GB engine).
+    need_host = (not args.no_e2e) or (rank == 0 and world == 1 and not (args.no_cpu_baseline and args.no_ref_gpu_engine))
+    h_vals = h_idx = h_norms = None
+    row_b, row_c = MuNmf.row_slice(n, world, rank)
+    if need_host:
+        h_vals = torch.empty((row_c, k), dtype=torch.float32, pin_memory=True)
+        h_idx = torch.empty((row_c, k), dtype=torch.int32, pin_memory=True)
+        h_norms = torch.empty((row_c,), dtype=torch.float32, pin_memory=True)
+        h_vals.copy_(d_vals[row_b:row_b + row_c])
+        h_idx.copy_(d_idx[row_b:row_b + row_c])
+        h_norms.copy_(d_norms[row_b:row_b + row_c])
+        torch.cuda.synchronize()
+
     eng = make_engine()
     t0 = time.perf_counter()
     eng.set_csr_device(n, m, d_vals.data_ptr(), d_idx.data_ptr(), 0, k, d_norms.data_ptr(), 1)
     t_load = time.perf_counter() - t0
+    del d_vals, d_idx, d_norms
+    torch.cuda.empty_cache()
     join(eng)
     eng.set_init_scale(global_scale(eng))
     eng.init_factors()
@@ -465,15 +483,8 @@ def main():
     # ---- e2e: host buffers -> loader -> K iterations -> W,H back, through the C ABI
     e2e = None
     if not args.no_e2e:
-        h_vals = torch.empty((n, k), dtype=torch.float32, pin_memory=True)
-        h_idx = torch.empty((n, k), dtype=torch.int32, pin_memory=True)
-        h_norms = torch.empty((n,), dtype=torch.float32, pin_memory=True)
-        h_vals.copy_(d_vals)
-        h_idx.copy_(d_idx)
-        h_norms.copy_(d_norms)
-        torch.cuda.synchronize()
-        del d_vals, d_idx
-        torch.cuda.empty_cache()
+        # every rank hands the loader the rows it holds in pinned host memory: the whole
+        # matrix on one GPU, its slice of the rows (dnpeff_row_slice) otherwise
         W_out = torch.empty((n, r), dtype=torch.float32, pin_memory=True)
         H_out = torch.empty((r, ms), dtype=torch.float32, pin_memory=True)
         eng2 = make_engine()
@@ -481,8 +492,8 @@ def main():
         barrier()
         ev0.record()
         tw = [time.perf_counter()]
-        check(lib().dnpeff_set_csr(eng2._h, n, m, k, None, h_vals.data_ptr(), h_idx.data_ptr(),
-                                   h_norms.data_ptr(), 1))
+        check(lib().dnpeff_set_csr_rows(eng2._h, n, m, k, row_b, row_c, None, h_vals.data_ptr(), h_idx.data_ptr(),
+                                        h_norms.data_ptr(), 1))
         tw.append(time.perf_counter())
         eng2.set_init_scale(global_scale(eng2))
         eng2.init_factors()
@@ -500,16 +511,23 @@ def main():
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ms = float(te.item())
+        # bytes of this rank; the job's total is the sum over the ranks
         h2d = h_vals.numel() * 4 + h_idx.numel() * 4 + h_norms.numel() * 4
         d2h = W_out.numel() * 4 + H_out.numel() * 4
+        tb = torch.tensor([h2d, d2h], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(tb)
+        h2d_job, d2h_job = float(tb[0].item()), float(tb[1].item())
         loss_k_e2e = eng2.compute_uncached_loss()
         e2e = {"value": args.steps / (e2e_ms * 1e-3), "unit": UNIT,
-               "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps,
+               "h2d_bytes_per_step": h2d_job / args.steps, "d2h_bytes_per_step": d2h_job / args.steps,
+               "h2d_bytes_per_step_per_rank": h2d / args.steps,
                "ms_total": e2e_ms,
                "host_ms": {"load": round(1e3 * (tw[1] - tw[0]), 1), "iterate": round(1e3 * (tw[2] - tw[1]), 1),
                            "read_back": round(1e3 * (tw[3] - tw[2]), 1)},
-               "what": "dnpeff_set_csr from pinned host arrays (upload, normalise, prune, shard, CSC) "
-                       "+ init + K iterations + dnpeff_get_w/get_h into pinned host arrays",
+               "what": "dnpeff_set_csr_rows from pinned host arrays: every rank uploads its 1/N of the rows; "
+                       "column counts all-reduced, entries exchanged over NVLink to the rank owning their column; "
+                       "normalise, prune, shard, CSC + init + K iterations + dnpeff_get_w/get_h into pinned host arrays",
                # the end-to-end run against the resident run after the same K iterations
                # from the same seeded factors (the slab-pipelined loader against the device loader)
                "self_check": {"loss_after_k_resident": loss_k_resident, "loss_after_k_e2e": loss_k_e2e,
@@ -526,9 +544,7 @@ def main():
     ref_gpu = None
     if rank == 0 and world == 1 and (not args.no_cpu_baseline or not args.no_ref_gpu_engine):
         if host_arrays is None:
-            host_arrays = (d_vals.cpu().numpy(), d_idx.cpu().numpy(), d_norms.cpu().numpy())
-            del d_vals, d_idx
-            torch.cuda.empty_cache()
+            host_arrays = (h_vals.numpy(), h_idx.numpy(), h_norms.numpy())
         if not args.no_ref_gpu_engine:
             ms_ref, why = ref_gpu_engine_ms_per_step(c, *host_arrays)
             ref_gpu = {"ms_per_step": ms_ref, "unavailable": why,
