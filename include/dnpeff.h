@@ -140,6 +140,18 @@ int dnpeff_set_csr_rows(dnpeff_engine* eng, int64_t n_rows_total, int64_t n_cols
                         int64_t row_begin, int64_t n_rows, const int64_t* rowptr, const float* vals,
                         const int32_t* colind, const float* norms, int32_t min_values_per_parameter);
 
+/* dnpeff_set_csr_rows with the slice already in device memory. */
+int dnpeff_set_csr_rows_device(dnpeff_engine* eng, int64_t n_rows_total, int64_t n_cols_full, int64_t k_per_row,
+                               int64_t row_begin, int64_t n_rows, const int64_t* d_rowptr, const float* d_vals,
+                               const int32_t* d_colind, const float* d_norms, int32_t min_values_per_parameter);
+/* shard_index / n_shards the engine was created with, and its device (any may be NULL). */
+int dnpeff_get_shard(dnpeff_engine* eng, int32_t* shard_index, int32_t* n_shards, int32_t* device);
+/* Collective AND over the engines of a job: *all_ok = 1 only if every engine passed
+ * ok != 0.  Lets the engines agree, before a collective loader call, that each of
+ * them could read its part of a file (an engine that stayed out of a collective
+ * would leave the others waiting).  No reference counterpart (single process). */
+int dnpeff_comm_agree(dnpeff_engine* eng, int32_t ok, int32_t* all_ok);
+
 /* The same loader with the kept columns given as a list of original column ids
  * instead of a count threshold: CsrMatrix::RetainColumns_InPlace
  * (src/cuda/host/sparse_matrix.h:141-170) as fit_coeffs_to_sparse_H applies it
@@ -189,8 +201,12 @@ int dnpeff_a_sum(dnpeff_engine* eng, double* out);
  * dnpeff_read_pef_hdf5 / dnpeff_load_pef_hdf5 replace PefSparseFishers::read
  * (:107-226): n_examples / n_fisher_values <= 0 mean "all", otherwise the leading
  * rows / leading values per row are taken (--n_examples, --n_fisher_values).
- * dnpeff_load_pef_hdf5 = read + dnpeff_set_csr.  Files are read and written by a
- * built-in HDF5 codec (contiguous, uncompressed datasets only). */
+ * dnpeff_load_pef_hdf5 = read + load, streamed: the engine reads only its slice of
+ * the rows (dnpeff_row_slice; the whole file for a single engine) in chunks into two
+ * page-locked staging buffers and uploads each chunk while the next is being read,
+ * then runs the row-sliced loader (dnpeff_set_csr_rows_device); a multi-engine job
+ * calls it on every engine after dnpeff_comm_init (collective).  Files are read and
+ * written by a built-in HDF5 codec (contiguous, uncompressed datasets only). */
 int dnpeff_pef_hdf5_info(const char* path, int64_t* n_examples, int64_t* n_values_per_example,
                          int64_t* dense_fisher_size);
 int dnpeff_read_pef_hdf5(const char* path, int64_t n_examples, int64_t n_fisher_values, float* vals,
@@ -269,6 +285,9 @@ int dnpeff_comm_init(dnpeff_engine* eng, const void* id128, int comm_rank, int c
 int dnpeff_step_w(dnpeff_engine* eng);
 int dnpeff_step_h(dnpeff_engine* eng);
 int dnpeff_run(dnpeff_engine* eng, int32_t iters, int32_t log_every);
+/* dnpeff_run for a run made in several calls (periodic checkpoints): the logged
+ * step numbers continue from first_step. */
+int dnpeff_run_steps(dnpeff_engine* eng, int32_t first_step, int32_t iters, int32_t log_every);
 int dnpeff_synchronize(dnpeff_engine* eng);
 /* computeUncachedLoss (multi_mu_dense_factors_nmf1.h:242-274): the global
  * sqrt(|A|^2 + <H,(W^T W)H> - 2<W^T A,H>), identical on every engine. */

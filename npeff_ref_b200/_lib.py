@@ -40,6 +40,10 @@ SIGNATURES = {
     "dnpeff_set_csr": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_row_slice": (C.c_int, [_I64, _I32, _I32, C.POINTER(_I64), C.POINTER(_I64)]),
     "dnpeff_set_csr_rows": (C.c_int, [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
+    "dnpeff_set_csr_rows_device": (C.c_int, [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
+    "dnpeff_get_shard": (C.c_int, [_P, C.POINTER(_I32), C.POINTER(_I32), C.POINTER(_I32)]),
+    "dnpeff_comm_agree": (C.c_int, [_P, _I32, C.POINTER(_I32)]),
+    "dnpeff_run_steps": (C.c_int, [_P, _I32, _I32, _I32]),
     "dnpeff_set_csr_device": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _I32]),
     "dnpeff_set_csr_retain": (C.c_int, [_P, _I64, _I64, _I64, _P, _P, _P, _P, _P, _I64]),
     "dnpeff_get_shape": (C.c_int, [_P] + [C.POINTER(_I64)] * 5),

@@ -1448,6 +1448,55 @@ int dnpeff_set_csr_rows(dnpeff_engine* e, int64_t n_rows_total, int64_t n_cols_f
                         nullptr, 0, n_rows_total, row_begin);
 }
 
+int dnpeff_set_csr_rows_device(dnpeff_engine* e, int64_t n_rows_total, int64_t n_cols_full, int64_t k_per_row,
+                               int64_t row_begin, int64_t n_rows, const int64_t* d_rowptr, const float* d_vals,
+                               const int32_t* d_colind, const float* d_norms, int32_t min_values_per_parameter) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    if (n_rows_total < 0 || n_rows < 0 || row_begin < 0 || row_begin + n_rows > n_rows_total)
+        return fail(DNPEFF_ERR_INVALID, "row slice outside the matrix");
+    DeviceGuard g(e->device);
+    int s;
+    if (e->p.n_shards == 1) {
+        if (row_begin != 0 || n_rows != n_rows_total)
+            return fail(DNPEFF_ERR_INVALID, "a single engine takes the whole matrix");
+        s = load_device(e, n_rows, n_cols_full, k_per_row, d_rowptr, d_vals, d_colind, d_norms, min_values_per_parameter);
+    } else {
+        if (e->comm_size != e->p.n_shards)
+            return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init first");
+        RowSlice slice = {n_rows, row_begin};
+        s = load_device(e, n_rows_total, n_cols_full, k_per_row, d_rowptr, d_vals, d_colind, d_norms,
+                        min_values_per_parameter, nullptr, 0, nullptr, &slice);
+    }
+    if (s != DNPEFF_OK) free_matrix(e);
+    return s;
+}
+
+int dnpeff_get_shard(dnpeff_engine* e, int32_t* shard_index, int32_t* n_shards, int32_t* device) {
+    if (!e) return fail(DNPEFF_ERR_INVALID, "null engine");
+    if (shard_index) *shard_index = e->p.shard_index;
+    if (n_shards) *n_shards = e->p.n_shards;
+    if (device) *device = e->device;
+    return DNPEFF_OK;
+}
+
+int dnpeff_comm_agree(dnpeff_engine* e, int32_t ok, int32_t* all_ok) {
+    if (!e || !all_ok) return fail(DNPEFF_ERR_INVALID, "null argument");
+    *all_ok = ok ? 1 : 0;
+    if (e->p.n_shards == 1) return DNPEFF_OK;
+    if (e->comm_size != e->p.n_shards)
+        return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init first");
+    DeviceGuard g(e->device);
+    DevBuf<int32_t> flag;
+    DN_TRY(flag.alloc(1));
+    int32_t h = ok ? 1 : 0;
+    DN_CUDA(cudaMemcpyAsync(flag.p, &h, sizeof(int32_t), cudaMemcpyHostToDevice, e->st));
+    DN_NCCL(nccl_api().AllReduce(flag.p, flag.p, 1, ncclInt32, ncclMin, e->comm, e->st));
+    DN_CUDA(cudaMemcpyAsync(&h, flag.p, sizeof(int32_t), cudaMemcpyDeviceToHost, e->st));
+    DN_CUDA(cudaStreamSynchronize(e->st));
+    *all_ok = h;
+    return DNPEFF_OK;
+}
+
 int dnpeff_set_csr_retain(dnpeff_engine* e, int64_t n_rows, int64_t n_cols_full, int64_t k_per_row,
                           const int64_t* rowptr, const float* vals, const int32_t* colind,
                           const float* norms, const int32_t* retained_cols, int64_t n_retained) {
@@ -1820,13 +1869,16 @@ int dnpeff_loss(dnpeff_engine* e, double* out) {
     return loss_from_current(e, true, out);
 }
 
-int dnpeff_run(dnpeff_engine* e, int32_t iters, int32_t log_every) {
+int dnpeff_run(dnpeff_engine* e, int32_t iters, int32_t log_every) { return dnpeff_run_steps(e, 0, iters, log_every); }
+
+int dnpeff_run_steps(dnpeff_engine* e, int32_t first_step, int32_t iters, int32_t log_every) {
     DN_TRY(check_ready(e, true));
     DeviceGuard g(e->device);
     if (e->p.n_shards > 1 && e->comm_size != e->p.n_shards)
         return fail(DNPEFF_ERR_INVALID, "sharded engine without a communicator: call dnpeff_comm_init");
+    if (first_step < 0) return fail(DNPEFF_ERR_INVALID, "negative first step");
     auto t0 = std::chrono::high_resolution_clock::now();
-    for (int step = 0; step < iters; step++) {
+    for (int step = first_step; step < first_step + iters; step++) {
         DN_TRY(step_w(e));
         DN_TRY(step_h(e));
         // "step N: <loss> [<ms> ms/step]" every log_every steps, loss time

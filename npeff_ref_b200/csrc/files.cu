@@ -1,6 +1,7 @@
 // File entry points of the C ABI: D-PEF input (src/io/pef_fisher_h5.h:57-226) and
 // decomposition output/input (src/io/nmf_decomp_h5.h:38-126) through the built-in
 // HDF5 codec.  Host code only.
+#include <algorithm>
 #include <vector>
 
 #include "../../include/dnpeff_synth.h"
@@ -67,35 +68,115 @@ int dnpeff_read_pef_hdf5(const char* path, int64_t n_examples, int64_t n_fisher_
     return DNPEFF_OK;
 }
 
+// PefSparseFishers::read (src/io/pef_fisher_h5.h:175-220) reads the whole file into
+// malloc'd arrays before anything is uploaded.  Here the engine's slice of the rows is
+// read in chunks into two page-locked staging buffers per dataset; chunk i crosses
+// PCIe while chunk i+1 is being read from the file, and no whole-file host copy exists.
 int dnpeff_load_pef_hdf5(dnpeff_engine* eng, const char* path, int64_t n_examples,
                          int64_t n_fisher_values, int32_t min_values_per_parameter) {
     if (!eng || !path) return fail(DNPEFF_ERR_INVALID, "null argument");
+    int32_t shard = 0, n_shards = 1, device = 0;
+    DN_TRY(dnpeff_get_shard(eng, &shard, &n_shards, &device));
+    // the staging and device buffers belong on the engine's device; the caller's
+    // current device is put back on return
+    struct DeviceScope {
+        int prev = -1;
+        explicit DeviceScope(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
+        ~DeviceScope() { if (prev >= 0) cudaSetDevice(prev); }
+    } device_scope(device);
     int64_t n = 0, k = 0, dense = 0;
-    DN_TRY(dnpeff_pef_hdf5_info(path, &n, &k, &dense));
-    if (n_examples > 0) {
-        if (n_examples > n) return fail(DNPEFF_ERR_INVALID, "--n_examples exceeds the file's %ld rows", (long)n);
+    int status = dnpeff_pef_hdf5_info(path, &n, &k, &dense);
+    if (status == DNPEFF_OK && n_examples > 0) {
+        if (n_examples > n) status = fail(DNPEFF_ERR_INVALID, "--n_examples exceeds the file's %ld rows", (long)n);
         n = n_examples;
     }
-    if (n_fisher_values > 0) {
-        if (n_fisher_values > k) return fail(DNPEFF_ERR_INVALID, "--n_fisher_values exceeds the file's %ld", (long)k);
+    if (status == DNPEFF_OK && n_fisher_values > 0) {
+        if (n_fisher_values > k) status = fail(DNPEFF_ERR_INVALID, "--n_fisher_values exceeds the file's %ld", (long)k);
         k = n_fisher_values;
     }
-    float* vals = nullptr;
-    int32_t* idx = nullptr;
-    float* norms = nullptr;
-    size_t nnz = (size_t)n * (size_t)k;
-    // pinned staging so the upload runs at full PCIe rate
-    if (cudaMallocHost((void**)&vals, sizeof(float) * (nnz ? nnz : 1)) != cudaSuccess ||
-        cudaMallocHost((void**)&idx, sizeof(int32_t) * (nnz ? nnz : 1)) != cudaSuccess ||
-        cudaMallocHost((void**)&norms, sizeof(float) * (size_t)(n ? n : 1)) != cudaSuccess) {
-        cudaFreeHost(vals); cudaFreeHost(idx); cudaFreeHost(norms);
-        return fail(DNPEFF_ERR_CUDA, "pinned host allocation for the D-PEF file failed");
+    int64_t row_begin = 0, rows = 0;
+    if (status == DNPEFF_OK) status = dnpeff_row_slice(n, n_shards, shard, &row_begin, &rows);
+
+    float *d_vals = nullptr, *d_norms = nullptr;
+    int32_t* d_idx = nullptr;
+    float* h_vals[2] = {nullptr, nullptr};
+    int32_t* h_idx[2] = {nullptr, nullptr};
+    float* h_norms = nullptr;
+    cudaStream_t up = nullptr;
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    char msg[1024] = {0};
+    auto keep_msg = [&]() { snprintf(msg, sizeof(msg), "%s", dnpeff_last_error()); };
+    if (status != DNPEFF_OK) keep_msg();
+
+    // about 64 MB per staging buffer
+    const int64_t chunk_rows = std::max<int64_t>(1, ((int64_t)64 << 20) / std::max<int64_t>(4 * k, 1));
+    if (status == DNPEFF_OK) {
+        const size_t cnt = (size_t)std::max<int64_t>(rows * k, 1), stage = (size_t)std::max<int64_t>(chunk_rows * k, 1);
+        bool ok = cudaMalloc((void**)&d_vals, sizeof(float) * cnt) == cudaSuccess &&
+                  cudaMalloc((void**)&d_idx, sizeof(int32_t) * cnt) == cudaSuccess &&
+                  cudaMalloc((void**)&d_norms, sizeof(float) * (size_t)std::max<int64_t>(rows, 1)) == cudaSuccess &&
+                  cudaMallocHost((void**)&h_norms, sizeof(float) * (size_t)std::max<int64_t>(rows, 1)) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&up, cudaStreamNonBlocking) == cudaSuccess;
+        for (int b2 = 0; b2 < 2 && ok; b2++)
+            ok = cudaMallocHost((void**)&h_vals[b2], sizeof(float) * stage) == cudaSuccess &&
+                 cudaMallocHost((void**)&h_idx[b2], sizeof(int32_t) * stage) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&done[b2], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {
+            cudaGetLastError();
+            status = fail(DNPEFF_ERR_CUDA, "device or page-locked memory for the D-PEF rows could not be allocated");
+            keep_msg();
+        }
     }
-    int s = dnpeff_read_pef_hdf5(path, n, k, vals, idx, norms);
-    if (s == DNPEFF_OK)
-        s = dnpeff_set_csr(eng, n, dense, k, nullptr, vals, idx, norms, min_values_per_parameter);
-    cudaFreeHost(vals); cudaFreeHost(idx); cudaFreeHost(norms);
-    return s;
+    if (status == DNPEFF_OK) {
+        try {
+            h5lite::Reader rd(path);
+            h5lite::ObjectInfo dv = rd.dataset("data/fisher/values"), di = rd.dataset("data/fisher/indices");
+            rd.read_block(rd.dataset("data/dense_fisher_norms"), (uint64_t)row_begin, (uint64_t)rows, 1, h5lite::DType::f32(),
+                          h_norms);
+            if (rows > 0 && cudaMemcpyAsync(d_norms, h_norms, sizeof(float) * (size_t)rows, cudaMemcpyHostToDevice, up) != cudaSuccess)
+                throw h5lite::Error("upload of the row norms failed");
+            int buf = 0;
+            for (int64_t r0 = 0; r0 < rows; r0 += chunk_rows, buf ^= 1) {
+                const int64_t nr = std::min(chunk_rows, rows - r0);
+                if (r0 >= 2 * chunk_rows) cudaEventSynchronize(done[buf]);  // the staging buffer's previous upload
+                rd.read_block(dv, (uint64_t)(row_begin + r0), (uint64_t)nr, (uint64_t)k, h5lite::DType::f32(), h_vals[buf]);
+                rd.read_block(di, (uint64_t)(row_begin + r0), (uint64_t)nr, (uint64_t)k, h5lite::DType::i32(), h_idx[buf]);
+                if (cudaMemcpyAsync(d_vals + r0 * k, h_vals[buf], sizeof(float) * (size_t)(nr * k), cudaMemcpyHostToDevice, up) != cudaSuccess ||
+                    cudaMemcpyAsync(d_idx + r0 * k, h_idx[buf], sizeof(int32_t) * (size_t)(nr * k), cudaMemcpyHostToDevice, up) != cudaSuccess ||
+                    cudaEventRecord(done[buf], up) != cudaSuccess)
+                    throw h5lite::Error("upload of a chunk of D-PEF rows failed");
+            }
+            if (cudaStreamSynchronize(up) != cudaSuccess) throw h5lite::Error("upload of the D-PEF rows failed");
+        } catch (const std::exception& ex) {
+            cudaGetLastError();
+            status = fail(DNPEFF_ERR_IO, "%s", ex.what());
+            keep_msg();
+        }
+    }
+    // every engine of the job gets here, whatever happened to its own part of the file,
+    // and they enter the collective loader only if all of them could read theirs
+    int32_t all_ok = 0;
+    int s2 = dnpeff_comm_agree(eng, status == DNPEFF_OK ? 1 : 0, &all_ok);
+    if (status == DNPEFF_OK && s2 != DNPEFF_OK) { status = s2; keep_msg(); }
+    if (status == DNPEFF_OK && !all_ok) {
+        status = fail(DNPEFF_ERR_IO, "another engine of the job could not read its rows of %s", path);
+        keep_msg();
+    }
+    if (status == DNPEFF_OK) {
+        status = dnpeff_set_csr_rows_device(eng, n, dense, k, row_begin, rows, nullptr, d_vals, d_idx, d_norms,
+                                            min_values_per_parameter);
+        if (status != DNPEFF_OK) keep_msg();
+    }
+    if (up) { cudaStreamSynchronize(up); cudaStreamDestroy(up); }
+    for (int b2 = 0; b2 < 2; b2++) {
+        if (done[b2]) cudaEventDestroy(done[b2]);
+        cudaFreeHost(h_vals[b2]);
+        cudaFreeHost(h_idx[b2]);
+    }
+    cudaFreeHost(h_norms);
+    cudaFree(d_vals); cudaFree(d_idx); cudaFree(d_norms);
+    if (status != DNPEFF_OK) return fail(status, "%s", msg);
+    return DNPEFF_OK;
 }
 
 int dnpeff_save_decomposition_hdf5(const char* path, const float* W, const float* H,

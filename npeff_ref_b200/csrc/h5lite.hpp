@@ -504,24 +504,41 @@ class Reader {
     // Reads the leading [rows x cols] block of a rank-2 dataset (or the leading
     // `rows` of a rank-1 one, cols = 1) into `out`, converting to `want`.
     void read_leading(const ObjectInfo& o, uint64_t rows, uint64_t cols, DType want, void* out) {
+        read_block(o, 0, rows, cols, want, out);
+    }
+
+    // Rows [row0, row0 + rows) and the leading `cols` columns of a rank-2 dataset (a
+    // rank-1 one: cols = 1) into `out`, converting to `want`.  When the stored type is
+    // the wanted one the bytes go straight from the file into `out`.
+    void read_block(const ObjectInfo& o, uint64_t row0, uint64_t rows, uint64_t cols, DType want, void* out) {
         uint64_t full_rows = 1, full_cols = 1;
         if (o.space.dims.size() == 1) { full_rows = o.space.dims[0]; full_cols = 1; }
         else if (o.space.dims.size() == 2) { full_rows = o.space.dims[0]; full_cols = o.space.dims[1]; }
         else if (!o.space.dims.empty()) throw Error("h5lite: rank > 2 datasets are not supported");
-        if (rows > full_rows || cols > full_cols) throw Error("h5lite: requested block exceeds the dataset");
+        if (row0 + rows > full_rows || cols > full_cols) throw Error("h5lite: requested block exceeds the dataset");
         if (rows == 0 || cols == 0) return;
         const size_t es = (size_t)o.type.size;
+        uint8_t* dst = (uint8_t*)out;
+        const bool same = !o.type.big_endian && o.type.cls == want.cls && o.type.size == want.size;
+        if (same) {
+            if (cols == full_cols) {
+                raw(o, (row0 * full_cols) * es, dst, (size_t)(rows * cols * es));
+            } else {
+                for (uint64_t r = 0; r < rows; r++)
+                    raw(o, ((row0 + r) * full_cols) * es, dst + (size_t)(r * cols * es), (size_t)(cols * es));
+            }
+            return;
+        }
         const uint64_t chunk_rows = std::max<uint64_t>(1, (64ull << 20) / std::max<uint64_t>(1, cols * es));
         std::vector<uint8_t> buf;
-        uint8_t* dst = (uint8_t*)out;
         for (uint64_t r0 = 0; r0 < rows; r0 += chunk_rows) {
             uint64_t nr = std::min(chunk_rows, rows - r0);
             buf.resize((size_t)(nr * cols * es));
             if (cols == full_cols) {
-                raw(o, (r0 * full_cols) * es, buf.data(), buf.size());
+                raw(o, ((row0 + r0) * full_cols) * es, buf.data(), buf.size());
             } else {
                 for (uint64_t r = 0; r < nr; r++)
-                    raw(o, ((r0 + r) * full_cols) * es, buf.data() + (size_t)(r * cols * es), (size_t)(cols * es));
+                    raw(o, ((row0 + r0 + r) * full_cols) * es, buf.data() + (size_t)(r * cols * es), (size_t)(cols * es));
             }
             convert(buf.data(), o.type, dst + (size_t)(r0 * cols * want.size), want, nr * cols);
         }

@@ -15,7 +15,18 @@
 // Extra, optional: --eps (1e-8) --seed (43190432042) --init_scale (1 = unscaled
 // uniform) --n_devices (all) --log_every (10) --shard_mode (cyclic|contiguous)
 // --sparsify_initial_W (0; 1 makes that call: with --sparsity_W > 0 the columns of
-// the initial W are projected onto L1 = sparsity_W, L2 = 1 before the first step).
+// the initial W are projected onto L1 = sparsity_W, L2 = 1 before the first step)
+// --checkpoint_every (0 = never; K > 0: after every K-th step the factors are written
+// to <output_path>.checkpoint -- a decomposition file like the output, written under
+// a temporary name and renamed, so a reader never sees half a file; a run continues
+// from it with --initial_W_path / --initial_H_path set to that file and
+// --nmf_max_iter set to the steps that remain, and ends bit for bit where the
+// uninterrupted run ends).
+//
+// Every engine reads only its own slice of the file's rows, in chunks through
+// page-locked staging buffers (dnpeff_load_pef_hdf5); the reference reads the whole
+// file into one host array first (src/io/pef_fisher_h5.h:175-220).
+#include <algorithm>
 #include <atomic>
 #include <condition_variable>
 #include <cstdio>
@@ -87,6 +98,7 @@ int main(int argc, char** argv) {
     g_argv = argv;
     std::string output_path, pef_path, init_h_path, init_w_path, shard_mode_s = "cyclic";
     int n_components = 0, max_iters = 0, min_values = 1, n_devices_flag = 0, log_every = 10, sparsify_initial_w = 0;
+    int checkpoint_every = 0;
     long long n_examples = -1, n_fisher_values = -1, seed = 43190432042ll;
     float sparsity_w = -1.f, eps = 1e-8f, init_scale = 0.f;
     flag_str("output_path", &output_path, true);
@@ -106,6 +118,7 @@ int main(int argc, char** argv) {
     flag_num("log_every", &log_every, false);
     flag_str("shard_mode", &shard_mode_s, false);
     flag_num("sparsify_initial_W", &sparsify_initial_w, false);
+    flag_num("checkpoint_every", &checkpoint_every, false);
     const int shard_mode = shard_mode_s == "contiguous" ? DNPEFF_SHARD_CONTIGUOUS : DNPEFF_SHARD_CYCLIC;
 
     int64_t n = 0, k = 0, dense = 0;
@@ -130,9 +143,6 @@ int main(int argc, char** argv) {
 
     printf("Reading in PEFs.\n");
     fflush(stdout);
-    std::vector<float> vals((size_t)n * k), norms((size_t)n);
-    std::vector<int32_t> idx((size_t)n * k);
-    if (dnpeff_read_pef_hdf5(pef_path.c_str(), n, k, vals.data(), idx.data(), norms.data())) die("reading the D-PEF file");
 
     // optional initial factors from an earlier decomposition file
     std::vector<float> W_init, H_init;
@@ -175,6 +185,26 @@ int main(int argc, char** argv) {
     std::string first_error;
     Barrier bar(n_dev);
 
+    // loadHToHostSync: the shards side by side in kept-column order, then the file
+    auto save_decomposition = [&](const std::string& path) -> bool {
+        std::vector<float> H((size_t)n_components * m_kept);
+        for (int d = 0; d < n_dev; d++)
+            for (int t = 0; t < n_components; t++)
+                for (int64_t j = 0; j < shards[d].ms; j++)
+                    H[(size_t)t * m_kept + shards[d].kept_ids[(size_t)j]] = shards[d].H[(size_t)t * shards[d].ms + j];
+        return dnpeff_save_decomposition_hdf5(path.c_str(), W.data(), H.data(), new_to_og.data(), n, n_components,
+                                              m_kept, dense) == DNPEFF_OK;
+    };
+    auto write_checkpoint = [&](int step) {
+        const std::string final_name = output_path + ".checkpoint", tmp_name = final_name + ".tmp";
+        if (!save_decomposition(tmp_name) || std::rename(tmp_name.c_str(), final_name.c_str()) != 0) {
+            fprintf(stderr, "run_nmf_on_pefs: checkpoint at step %d could not be written: %s\n", step, dnpeff_last_error());
+            return;  // the run itself goes on
+        }
+        printf("Checkpoint after step %d written to %s\n", step, final_name.c_str());
+        fflush(stdout);
+    };
+
     auto worker = [&](int d) {
         auto fail_here = [&](const char* what) {
             std::lock_guard<std::mutex> lk(err_mu);
@@ -185,7 +215,12 @@ int main(int argc, char** argv) {
         dnpeff_engine* eng = nullptr;
         bool ok = dnpeff_create(&p, d, nullptr, &eng) == DNPEFF_OK;
         if (!ok) fail_here("creating the engine");
-        if (ok && dnpeff_set_csr(eng, n, dense, k, nullptr, vals.data(), idx.data(), norms.data(), min_values)) {
+        bar.wait();  // nobody joins the communicator if an engine could not be made
+        if (failed) { if (eng) dnpeff_destroy(eng); return; }
+        if (n_dev > 1 && dnpeff_comm_init(eng, nccl_id, d, n_dev)) { fail_here("joining the communicator"); std::exit(1); }
+        // every engine streams its own slice of the rows from the file; the engines
+        // agree on the outcome of the reads before the collective part of the load
+        if (dnpeff_load_pef_hdf5(eng, pef_path.c_str(), n, k, min_values)) {
             ok = false;
             fail_here("loading the matrix");
         }
@@ -205,7 +240,6 @@ int main(int argc, char** argv) {
         }
         bar.wait();  // nobody enters a collective if anybody failed so far
         if (failed) { if (eng) dnpeff_destroy(eng); return; }
-        if (n_dev > 1 && dnpeff_comm_init(eng, nccl_id, d, n_dev)) { fail_here("joining the communicator"); std::exit(1); }
         // initial factors: generated, or taken from the files
         std::vector<float> Hs;
         if (!H_init.empty()) {
@@ -235,10 +269,28 @@ int main(int argc, char** argv) {
             }
         }
         if (d == 0) { printf("Running NMF.\n"); fflush(stdout); }
-        if (dnpeff_run(eng, max_iters, log_every)) { fail_here("running the NMF"); fprintf(stderr, "%s\n", first_error.c_str()); std::exit(1); }
         shards[d].H.resize((size_t)n_components * ms);
-        if (d == 0 && dnpeff_get_w(eng, W.data())) { fail_here("reading W"); std::exit(1); }
-        if (dnpeff_get_h(eng, shards[d].H.data())) { fail_here("reading H"); std::exit(1); }
+        auto read_factors = [&]() {
+            if (d == 0 && dnpeff_get_w(eng, W.data())) { fail_here("reading W"); std::exit(1); }
+            if (dnpeff_get_h(eng, shards[d].H.data())) { fail_here("reading H"); std::exit(1); }
+        };
+        // the run, in stretches of --checkpoint_every steps when that is set
+        for (int done = 0; done < max_iters;) {
+            const int stretch = checkpoint_every > 0 ? std::min(checkpoint_every, max_iters - done) : max_iters - done;
+            if (dnpeff_run_steps(eng, done, stretch, log_every)) {
+                fail_here("running the NMF");
+                fprintf(stderr, "%s\n", first_error.c_str());
+                std::exit(1);
+            }
+            done += stretch;
+            if (checkpoint_every > 0 && done < max_iters) {
+                read_factors();
+                bar.wait();  // every shard of H is on the host
+                if (d == 0) write_checkpoint(done);
+                bar.wait();  // the host buffers may be overwritten again
+            }
+        }
+        read_factors();
         dnpeff_destroy(eng);
     };
 
@@ -250,17 +302,8 @@ int main(int argc, char** argv) {
         return 1;
     }
 
-    // loadHToHostSync: the shards side by side in kept-column order
-    std::vector<float> H((size_t)n_components * m_kept);
-    for (int d = 0; d < n_dev; d++)
-        for (int t = 0; t < n_components; t++)
-            for (int64_t j = 0; j < shards[d].ms; j++)
-                H[(size_t)t * m_kept + shards[d].kept_ids[(size_t)j]] = shards[d].H[(size_t)t * shards[d].ms + j];
-
     printf("Saving decomposition to file.\n");
     fflush(stdout);
-    if (dnpeff_save_decomposition_hdf5(output_path.c_str(), W.data(), H.data(), new_to_og.data(), n,
-                                       n_components, m_kept, dense))
-        die("saving the decomposition");
+    if (!save_decomposition(output_path)) die("saving the decomposition");
     return 0;
 }

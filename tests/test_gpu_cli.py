@@ -96,6 +96,50 @@ def test_cli_resume_from_initial_factor_files(tmp_path):
     assert np.array_equal(kb, kf) and np.array_equal(Wb, Wf) and np.array_equal(Hb, Hf)
 
 
+def test_cli_periodic_checkpoint_resumes_bit_for_bit(tmp_path):
+    """--checkpoint_every=K writes <output_path>.checkpoint after every K-th step (a
+    decomposition file, written under a temporary name and renamed).  A run continued
+    from the checkpoint of step 10 for the remaining 10 steps ends exactly where the
+    uninterrupted 20-step run ends, and the step numbers of the log continue."""
+    n, m, k, r = 100, 3000, 80, 12
+    vals, idx, norms = make_problem(n, m, k, seed=64)
+    pef = str(tmp_path / "pef.h5")
+    _write_pef(pef, vals, idx, norms, m)
+    common = ["--per_example_fishers=" + pef, "--nmf_n_components=%d" % r, "--n_devices=1"]
+    full, part, cont = str(tmp_path / "full.h5"), str(tmp_path / "part.h5"), str(tmp_path / "cont.h5")
+    out_full = _run(*common, "--output_path=" + full, "--nmf_max_iter=20", "--checkpoint_every=10")
+    assert "Checkpoint after step 10 written to " + full + ".checkpoint" in out_full
+    assert [int(x) for x in re.findall(r"^step (\d+):", out_full, flags=re.M)] == [10, 20]
+    assert os.path.exists(full + ".checkpoint") and not os.path.exists(full + ".checkpoint.tmp")
+    # the checkpoint IS the state after 10 steps ...
+    _run(*common, "--output_path=" + part, "--nmf_max_iter=10", "--log_every=0")
+    Wc, Hc, kc, _ = _read_decomp(full + ".checkpoint")
+    Wp, Hp, kp, _ = _read_decomp(part)
+    assert np.array_equal(kc, kp) and np.array_equal(Wc, Wp) and np.array_equal(Hc, Hp)
+    # ... and a run continued from it ends where the uninterrupted one ends
+    ck = full + ".checkpoint"
+    _run(*common, "--output_path=" + cont, "--nmf_max_iter=10", "--initial_W_path=" + ck, "--initial_H_path=" + ck,
+         "--log_every=0")
+    Wf, Hf, kf, _ = _read_decomp(full)
+    Wr, Hr, kr, _ = _read_decomp(cont)
+    assert np.array_equal(kf, kr) and np.array_equal(Wf, Wr) and np.array_equal(Hf, Hr)
+
+
+def test_cli_truncated_input_file_fails_cleanly(tmp_path):
+    """A D-PEF file cut short (host-side fault injection): the executable reports the
+    read error and exits non-zero; nothing hangs and nothing is written."""
+    n, m, k = 60, 1000, 50
+    vals, idx, norms = make_problem(n, m, k, seed=65)
+    pef, cut, out = str(tmp_path / "pef.h5"), str(tmp_path / "cut.h5"), str(tmp_path / "nmf.h5")
+    _write_pef(pef, vals, idx, norms, m)
+    data = open(pef, "rb").read()
+    open(cut, "wb").write(data[:len(data) - 8000])
+    res = subprocess.run([CLI, "--per_example_fishers=" + cut, "--output_path=" + out, "--nmf_n_components=4",
+                          "--nmf_max_iter=2"], capture_output=True, text=True, timeout=300)
+    assert res.returncode != 0 and not os.path.exists(out)
+    assert "run_nmf_on_pefs" in res.stderr
+
+
 def test_cli_missing_required_flag_aborts():
     res = subprocess.run([CLI, "--output_path=/tmp/x.h5"], capture_output=True, text=True)
     assert res.returncode != 0 and "Missing flag: per_example_fishers" in res.stdout
