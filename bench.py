@@ -36,7 +36,7 @@ CONFIGS = {
     3: dict(n=50000, m=16777216, k=65536, r=256, alpha=1.1, sigma=1.0, seed=2),
     5: dict(n=50000, m=8388608, k=65536, r=512, alpha=1.4, sigma=2.0, seed=4),
     # coefficient fit only (H fixed, 90 % of it zero; W updated): not a headline line, a
-    # measurement of the W-only path on one GPU (use --scale-rows: the full n needs 8 GPUs' memory)
+    # measurement of the W-only path; on N GPUs the examples are split by rows, no exchange
     4: dict(n=200000, m=4194304, k=32768, r=256, alpha=1.1, sigma=1.0, seed=3, w_only=True),
 }
 EPS = 1e-12
@@ -243,44 +243,66 @@ def ref_gpu_engine_ms_per_step(c, h_vals, h_idx, h_norms, iters=10):
 # ---------------------------------------------------------------------------
 def run_w_only(args, c, cfg_id):
     """Config 4: H fixed (Uniform(0,1), 90 % zeroed), `steps` W-only multiplicative updates
-    (`dnpeff_fit_w_only`: A*H^T and H*H^T once, then W *= AH / (W*HH + eps) per step).  One
-    GPU; the rows of the full configuration would be split over GPUs with no exchange."""
+    (`dnpeff_fit_w_only`: A*H^T and H*H^T once, then W *= AH / (W*HH + eps) per step).  The
+    rows of W are independent given H, so on N GPUs the examples are split by rows
+    (dnpeff_row_slice), H is replicated and there is no exchange at all: every rank runs
+    its own engine; the job's rate is that of the slowest rank."""
     import torch
+    import torch.distributed as dist
     from npeff_ref_b200 import MuNmf, MuNmfParams
     from npeff_ref_b200._lib import lib, check
-    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
-        raise SystemExit("config 4 runs on one GPU (row chunks are independent: replicas only)")
-    torch.cuda.set_device(0)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     n, m, k, r = c["n"], c["m"], c["k"], c["r"]
+    row_b, row_c = MuNmf.row_slice(n, world, rank)
     side = torch.cuda.Stream()
     torch.cuda.set_stream(side)
     stream = side.cuda_stream
-    d_vals = torch.empty((n, k), dtype=torch.float32, device="cuda")
-    d_idx = torch.empty((n, k), dtype=torch.int32, device="cuda")
-    d_norms = torch.empty((n,), dtype=torch.float32, device="cuda")
-    check(lib().dnpeff_synth_pef_device(n, m, k, c["alpha"], c["sigma"], c["seed"], d_vals.data_ptr(),
-                                        d_idx.data_ptr(), d_norms.data_ptr(), stream))
-    eng = MuNmf(MuNmfParams(rank=r, eps=1e-7, seed=c["seed"]), device=0, stream=stream)
-    eng.set_csr_device(n, m, d_vals.data_ptr(), d_idx.data_ptr(), 0, k, d_norms.data_ptr(), 1)
+    d_vals = torch.empty((row_c, k), dtype=torch.float32, device="cuda")
+    d_idx = torch.empty((row_c, k), dtype=torch.int32, device="cuda")
+    d_norms = torch.empty((row_c,), dtype=torch.float32, device="cuda")
+    check(lib().dnpeff_synth_pef_device_rows(row_b, row_c, m, k, c["alpha"], c["sigma"], c["seed"], d_vals.data_ptr(),
+                                             d_idx.data_ptr(), d_norms.data_ptr(), stream))
+    eng = MuNmf(MuNmfParams(rank=r, eps=1e-7, seed=c["seed"]), device=local_rank, stream=stream)
+    # every column is kept (threshold 0), as with the retained-column list of a decomposition
+    # file: all ranks then share one H
+    eng.set_csr_device(row_c, m, d_vals.data_ptr(), d_idx.data_ptr(), 0, k, d_norms.data_ptr(), 0)
+    del d_vals, d_idx, d_norms
+    torch.cuda.empty_cache()
     _, m_kept, _, ms, nnz = eng.shape
     g = torch.Generator(device="cuda").manual_seed(c["seed"])
     H = torch.rand((r, ms), generator=g, device="cuda")
     H = (H * (torch.rand((r, ms), generator=g, device="cuda") > 0.9)).cpu().numpy()
+    check(lib().dnpeff_set_w_row_offset(eng._h, row_b))   # W rows as the unsplit run would draw them
     eng.init_factors(None, H)
     del H
 
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     def timed(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
+        barrier()
         e0.record()
         eng.fit_w_only(iters, want_loss=False)
         e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1)
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     for _ in range(max(args.warmup, 3)):
         timed(1)
-    sampler = ClockSampler(physical_gpu_index(0))
+    sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
     launches0 = eng.launch_count()
     stage1 = min(timed(0) for _ in range(3))           # A*H^T + H*H^T alone
@@ -288,21 +310,31 @@ def run_w_only(args, c, cfg_id):
     launches = eng.launch_count() - launches0
     clocks = sampler.stop()
     per_step = max(total - stage1, 0.0) / max(args.steps, 1)
-    loss = eng.fit_w_only(0)
-    print(json.dumps({
-        "metric": "dnpeff_w_only_fit_iterations_per_s", "value": 1e3 / per_step if per_step > 0 else None,
-        "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(cfg_id, c).replace("eps=%g" % EPS, "eps=1e-07") + " W-only, H 90% zero", "n_cols_kept": m_kept,
-                   "nnz_per_rank": nnz, "stage1_ms": stage1, "loss_after": loss,
-                   "l2": "inputs larger than L2 (A %.1f GB, H %.2f GB)" % (16.0 * nnz / 1e9, 4.0 * r * ms / 1e9)},
-        "roofline": {"bound": "hbm", "kernel": "mu_update (W side)", "achieved": 3 * 4.0 * n * r / (per_step * 1e-3) / 1e9
-                     if per_step > 0 else None, "peak": measured_peak_hbm()[0], "unit": "GB/s",
-                     "frac": (3 * 4.0 * n * r / (per_step * 1e-3) / 1e9) / measured_peak_hbm()[0] if per_step > 0 else None,
-                     "peak_kind": "of " + measured_peak_hbm()[1], "traffic": None,
-                     "algorithmic_bytes_per_launch": 3 * 4.0 * n * r},
-        "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clocks}), flush=True)
+    # loss of the whole job: the row blocks' squared losses add
+    l2 = torch.tensor([eng.fit_w_only(0) ** 2, float(nnz)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(l2)
+    loss, nnz_job = math.sqrt(float(l2[0].item())), int(l2[1].item())
+    if rank == 0:
+        upd_bytes = 3 * 4.0 * row_c * r
+        print(json.dumps({
+            "metric": "dnpeff_w_only_fit_iterations_per_s", "value": 1e3 / per_step if per_step > 0 else None,
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(cfg_id, c).replace("eps=%g" % EPS, "eps=1e-07") + " W-only, H 90% zero",
+                       "n_cols_kept": m_kept, "nnz": nnz_job, "rows_per_rank": row_c, "shard": "rows/%d, no exchange" % world,
+                       "stage1_ms": stage1, "stage1_spmm_GBps": (8.0 * nnz + 4.0 * r * ms + 4.0 * row_c * r) / (stage1 * 1e-3) / 1e9,
+                       "loss_after": loss,
+                       "l2": "inputs larger than L2 (A %.1f GB, H %.2f GB per rank)" % (8.0 * nnz / 1e9, 4.0 * r * ms / 1e9)},
+            "roofline": {"bound": "hbm", "kernel": "mu_update (W side)", "achieved": upd_bytes / (per_step * 1e-3) / 1e9
+                         if per_step > 0 else None, "peak": measured_peak_hbm()[0], "unit": "GB/s",
+                         "frac": (upd_bytes / (per_step * 1e-3) / 1e9) / measured_peak_hbm()[0] if per_step > 0 else None,
+                         "peak_kind": "of " + measured_peak_hbm()[1], "traffic": None,
+                         "algorithmic_bytes_per_launch": upd_bytes},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clocks}), flush=True)
     eng.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():

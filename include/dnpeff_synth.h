@@ -24,6 +24,12 @@ int dnpeff_synth_pef_device(int64_t n_rows, int64_t n_cols, int64_t k_per_row, d
                             double sigma, uint64_t seed, float* d_vals, int32_t* d_idx,
                             float* d_norms, void* stream);
 
+/* Rows [row_first, row_first + n_rows) of the same matrix (a row's content depends on
+ * its index and the seed only): what one rank of a row-split job generates. */
+int dnpeff_synth_pef_device_rows(int64_t row_first, int64_t n_rows, int64_t n_cols, int64_t k_per_row,
+                                 double alpha, double sigma, uint64_t seed, float* d_vals, int32_t* d_idx,
+                                 float* d_norms, void* stream);
+
 /* Writes host arrays as a D-PEF file in the layout of
  * npeff/fishers/d_pefs_computer.py:235-251 (what dnpeff_load_pef_hdf5 and the
  * reference's PefSparseFishers::read consume).  The reference has no C++ writer

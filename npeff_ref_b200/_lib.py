@@ -92,6 +92,8 @@ SIGNATURES = {
     "dnpeff_hdf5_read_f64": (C.c_int, [C.c_char_p, C.c_char_p, _I64, _I64, _P]),
     "dnpeff_write_pef_hdf5": (C.c_int, [C.c_char_p, _I64, _I64, _P, _P, _P, _I64]),
     "dnpeff_op_gram_noalloc": (C.c_int, [_P, _I64, _I32, _P, _P]),
+    "dnpeff_synth_pef_device_rows": (C.c_int, [_I64, _I64, _I64, _I64, C.c_double, C.c_double, C.c_uint64,
+                                               _P, _P, _P, _P]),
     "dnpeff_synth_pef_device": (C.c_int, [_I64, _I64, _I64, C.c_double, C.c_double, C.c_uint64,
                                           _P, _P, _P, _P]),
 }

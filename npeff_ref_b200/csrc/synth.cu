@@ -41,7 +41,7 @@ __device__ __forceinline__ uint32_t perm_bits(uint32_t x, int bits, uint32_t key
 }
 
 __global__ void __launch_bounds__(kSynthThreads)
-k_synth_rows(int64_t n, int64_t m, int k, const double* __restrict__ cdf, double sigma,
+k_synth_rows(int64_t row_first, int64_t n, int64_t m, int k, const double* __restrict__ cdf, double sigma,
              uint64_t seed, uint32_t* __restrict__ bitmaps, int64_t bitmap_words,
              int32_t* __restrict__ claimed_all, float* __restrict__ out_vals,
              int32_t* __restrict__ out_idx, float* __restrict__ out_norms) {
@@ -56,8 +56,9 @@ k_synth_rows(int64_t n, int64_t m, int k, const double* __restrict__ cdf, double
     int bits = 1;
     while ((1ll << bits) < k) bits++;
 
+    // output row `row` is row row_first + row of the matrix: its draws depend on that index only
     for (int64_t row = blockIdx.x; row < n; row += gridDim.x) {
-        const uint64_t rkey = mix64(stream_key(seed, 2) + (uint64_t)row);
+        const uint64_t rkey = mix64(stream_key(seed, 2) + (uint64_t)(row_first + row));
         if (tid == 0) s_count = 0;
         __syncthreads();
         // ---- k distinct columns --------------------------------------------
@@ -208,7 +209,14 @@ k_synth_rows(int64_t n, int64_t m, int k, const double* __restrict__ cdf, double
 extern "C" int dnpeff_synth_pef_device(int64_t n_rows, int64_t n_cols, int64_t k_per_row,
                                        double alpha, double sigma, uint64_t seed, float* d_vals,
                                        int32_t* d_idx, float* d_norms, void* stream) {
-    if (n_rows < 0 || n_cols <= 0 || k_per_row <= 0 || k_per_row > n_cols || k_per_row > (1 << 30))
+    return dnpeff_synth_pef_device_rows(0, n_rows, n_cols, k_per_row, alpha, sigma, seed, d_vals, d_idx, d_norms,
+                                        stream);
+}
+
+extern "C" int dnpeff_synth_pef_device_rows(int64_t row_first, int64_t n_rows, int64_t n_cols, int64_t k_per_row,
+                                            double alpha, double sigma, uint64_t seed, float* d_vals,
+                                            int32_t* d_idx, float* d_norms, void* stream) {
+    if (row_first < 0 || n_rows < 0 || n_cols <= 0 || k_per_row <= 0 || k_per_row > n_cols || k_per_row > (1 << 30))
         return fail(DNPEFF_ERR_INVALID, "bad synthetic shape (need 0 < k <= n_cols)");
     if (n_cols >= INT32_MAX) return fail(DNPEFF_ERR_UNSUPPORTED, "n_cols must fit int32");
     if (n_rows == 0) return DNPEFF_OK;
@@ -234,7 +242,7 @@ extern "C" int dnpeff_synth_pef_device(int64_t n_rows, int64_t n_cols, int64_t k
         }
         cudaMemcpyAsync(d_cdf, cdf.data(), sizeof(double) * (size_t)n_cols, cudaMemcpyHostToDevice, st);
         cudaMemsetAsync(d_bitmaps, 0, sizeof(uint32_t) * (size_t)(words * grid), st);
-        k_synth_rows<<<grid, kSynthThreads, 0, st>>>(n_rows, n_cols, (int)k_per_row, d_cdf, sigma, seed,
+        k_synth_rows<<<grid, kSynthThreads, 0, st>>>(row_first, n_rows, n_cols, (int)k_per_row, d_cdf, sigma, seed,
                                                     d_bitmaps, words, d_claimed, d_vals, d_idx, d_norms);
         DN_COUNT_LAUNCH(1);
         cudaError_t e = cudaStreamSynchronize(st);

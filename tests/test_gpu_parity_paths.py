@@ -218,6 +218,29 @@ def test_host_generator_twin_matches_device_generator(torch_cuda):
         assert np.allclose(norms.cpu().numpy(), hn, rtol=2e-6)
 
 
+def test_device_generator_row_ranges_are_slices_of_the_matrix(torch_cuda):
+    """dnpeff_synth_pef_device_rows: a row's content depends on its index and the seed
+    only, so a rank of a row-split job generates exactly its slice of the matrix."""
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    n, m, k = 37, 9000, 512
+    st = torch.cuda.current_stream().cuda_stream
+
+    def gen(first, rows):
+        v = torch.empty((rows, k), dtype=torch.float32, device="cuda")
+        i = torch.empty((rows, k), dtype=torch.int32, device="cuda")
+        nr = torch.empty((rows,), dtype=torch.float32, device="cuda")
+        check(lib().dnpeff_synth_pef_device_rows(first, rows, m, k, 1.1, 1.0, 3, v.data_ptr(), i.data_ptr(),
+                                                 nr.data_ptr(), st))
+        return v.cpu().numpy(), i.cpu().numpy(), nr.cpu().numpy()
+
+    fv, fi, fn = gen(0, n)
+    for first, rows in [(0, 10), (10, 20), (30, 7)]:
+        v, i, nr = gen(first, rows)
+        assert np.array_equal(v, fv[first:first + rows]) and np.array_equal(i, fi[first:first + rows])
+        assert np.array_equal(nr, fn[first:first + rows])
+
+
 # ---------------------------------------------------------------------------
 def test_bounded_wait_runs_out_and_engine_recovers(torch_cuda):
     """The only device-side failure detection in the product: every wait between the
