@@ -270,3 +270,47 @@ def test_hoyer_empty_and_degenerate():
     # one row: the only vector with that L1 norm
     S, p, c = O.hoyer_project(np.array([[0.3, 0.9]], np.float32), 2.0, 1.0)
     assert c and np.allclose(S, 2.0)
+
+
+def test_host_generator_twin_properties():
+    """oracle.synth_pef_hashed (the host twin of the device generator the benchmark
+    uses): k distinct columns per row, values descending and non-negative, norms = L2
+    norms, deterministic in the seed, Zipf head present in (nearly) every row, and a
+    row's content independent of how many rows are generated."""
+    n, m, k = 24, 20000, 1024
+    v, i, nr = O.synth_pef_hashed(n, m, k, alpha=1.1, sigma=1.0, seed=5)
+    assert i.min() >= 0 and i.max() < m
+    for row in range(n):
+        assert len(np.unique(i[row])) == k
+        assert np.all(np.diff(v[row]) <= 0) and v[row, -1] >= 0
+    assert np.allclose(nr, np.sqrt((v.astype(np.float64) ** 2).sum(1)), rtol=1e-6)
+    assert np.mean([(0 in set(r_)) for r_ in i]) > 0.9
+    v2, i2, nr2 = O.synth_pef_hashed(n, m, k, alpha=1.1, sigma=1.0, seed=5)
+    assert np.array_equal(v, v2) and np.array_equal(i, i2) and np.array_equal(nr, nr2)
+    v3, i3, _ = O.synth_pef_hashed(7, m, k, alpha=1.1, sigma=1.0, seed=5)
+    assert np.array_equal(v3, v[:7]) and np.array_equal(i3, i[:7])
+    v4, i4, _ = O.synth_pef_hashed(n, m, k, alpha=1.1, sigma=1.0, seed=6)
+    assert not np.array_equal(i4, i)
+    # k == m: every column, whatever the draws
+    v5, i5, _ = O.synth_pef_hashed(3, 64, 64, seed=1)
+    assert all(sorted(r_) == list(range(64)) for r_ in i5)
+
+
+def test_problem_steps_match_run():
+    """oracle.Problem (what the timed CPU arm iterates) against oracle.run on the same
+    preprocessed matrix and seeded factors."""
+    n, m, k, r = 40, 3000, 100, 8
+    v, i, nr = O.synth_pef_hashed(n, m, k, seed=2)
+    rowptr = np.arange(n + 1, dtype=np.int64) * k
+    vn = O.normalize_rows(v.ravel(), rowptr, nr)
+    pv, pc, prp, n2o = O.prune_columns(vn, i.ravel(), rowptr, m, 1)
+    mk = len(n2o)
+    scale = float(np.float32(np.sqrt(pv.astype(np.float64).sum() / (n * mk) / r)))
+    W0, H0 = O.init_factors(n, mk, r, 2, scale)
+    _, _, ls = O.run(pv, pc, prp, mk, W0, H0, 3, 1e-12, acc64=False, losses=True)
+    P = O.Problem(n, m, k, r, v, i, nr, min_count=1, eps=1e-12, seed=2)
+    assert P.m_kept == mk
+    for step in range(3):
+        P.step(acc64=False)
+        assert abs(P.loss() - ls[step]) < 1e-6 * ls[step]
+    P.close()
