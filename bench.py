@@ -497,6 +497,14 @@ def main():
         "traffic": NCU_TRAFFIC_BYTES.get((cfg_id, world, dom)),
         "algorithmic_bytes_per_launch": spmm_bytes,
         "ms_per_launch": {a: (round(b, 4) if b is not None else None) for a, b in per_kernel.items()},
+        # what actually bounds the product at r >= 64: the tail entries' gather of one
+        # 4r-byte factor row each through the L2->SM read ports (64 B/clk/SM).  Lower bound
+        # of the rate: the whole product's time is charged to the gather, although the
+        # dense popular block (tensor cores) is part of it.
+        "l2_gather": {"bytes_per_launch": 4.0 * r * (nnz - layout[1]),
+                      "achieved_TBps_lower_bound": 4.0 * r * (nnz - layout[1]) / (per_kernel[dom] * 1e-3) / 1e12,
+                      "port_peak_TBps": 148 * 64 * (clocks["sm_mhz"] or 1965.0) * 1e6 / 1e12,
+                      "what": "tail entries x 4r bytes / product time, against 148 SMs x 64 B/clk at the sampled SM clock"},
         "note": "one product = the dense popular block on tensor cores + one launch per tail column block, timed as a whole; "
                 "every stored entry gathers r floats on chip (shared memory or L2), so the SpMM is not "
                 "HBM-bound for r >= 64; traffic is scaled from a small-case capture",

@@ -1825,15 +1825,19 @@ int dnpeff_comm_init(dnpeff_engine* e, const void* id128, int comm_rank, int com
     e->a_sq_global = -1.0;
     // NCCL connects its channels on the first collective (hundreds of ms): do that
     // here, as part of joining, not inside the first iteration
+    // ... and the point-to-point channels the row-sliced loader uses: NCCL opens as many
+    // channels per peer as a transfer's size calls for, the first time it is that large,
+    // so the first exchange here is of the loader's order of size (4 MB per peer), not a
+    // token one
+    const size_t kWarm = (size_t)1 << 20;  // floats per peer and direction
     DevBuf<float> one;
-    DN_TRY(one.alloc_zero(32 * (size_t)(2 * comm_size + 1), e->st));
+    DN_TRY(one.alloc_zero(32 + 2 * kWarm * (size_t)comm_size, e->st));
     DN_NCCL(nccl_api().AllReduce(one.p, one.p, 32, ncclFloat, ncclSum, e->comm, e->st));
-    // ... and the point-to-point channels the row-sliced loader uses on its first send / receive
     DN_NCCL(nccl_api().GroupStart());
     for (int d = 0; d < comm_size; d++) {
         if (d == comm_rank) continue;
-        DN_NCCL(nccl_api().Send(one.p + 32 * (size_t)(1 + d), 32, ncclFloat, d, e->comm, e->st));
-        DN_NCCL(nccl_api().Recv(one.p + 32 * (size_t)(1 + comm_size + d), 32, ncclFloat, d, e->comm, e->st));
+        DN_NCCL(nccl_api().Send(one.p + 32 + kWarm * (size_t)d, kWarm, ncclFloat, d, e->comm, e->st));
+        DN_NCCL(nccl_api().Recv(one.p + 32 + kWarm * (size_t)(comm_size + d), kWarm, ncclFloat, d, e->comm, e->st));
     }
     DN_NCCL(nccl_api().GroupEnd());
     DN_CUDA(cudaStreamSynchronize(e->st));
