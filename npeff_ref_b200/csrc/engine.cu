@@ -564,8 +564,20 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
     // lengths travel to d, which puts the slices of all engines one after the other.
     const int G = slice ? e->comm_size : 1;
     std::vector<ShardMap> map_of((size_t)G);
-    std::vector<DevBuf<int32_t>> rc_to((size_t)(slice ? G : 0));
-    std::vector<DevBuf<int64_t>> off_to((size_t)(slice ? G : 0));
+    // (one allocation each for all destinations: device allocations are driver calls
+    // that the processes of a box serialise on)
+    DevBuf<int32_t> rc_all;
+    DevBuf<int64_t> off_all;
+    std::vector<int32_t*> rc_to((size_t)G, nullptr);
+    std::vector<int64_t*> off_to((size_t)G, nullptr);
+    if (slice) {
+        DN_TRY(rc_all.alloc_zero((size_t)G * ((size_t)n_in + 1), st));
+        DN_TRY(off_all.alloc((size_t)G * ((size_t)n_in + 1)));
+        for (int d = 0; d < G; d++) {
+            rc_to[(size_t)d] = rc_all.p + (size_t)d * ((size_t)n_in + 1);
+            off_to[(size_t)d] = off_all.p + (size_t)d * ((size_t)n_in + 1);
+        }
+    }
     std::vector<int64_t> send_count((size_t)G, 0), slice_begin((size_t)G + 1, 0);
     if (slice) {
         for (int d = 0; d < G; d++) {
@@ -580,17 +592,24 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             int64_t sb = 0, sc = 0;
             row_slice(n, G, d, &sb, &sc);
             slice_begin[(size_t)d] = sb;
-            DN_TRY(rc_to[(size_t)d].alloc_zero((size_t)n_in + 1, st));
-            DN_TRY(off_to[(size_t)d].alloc((size_t)n_in + 1));
             if (n_in > 0) {
                 int64_t blocks = std::min<int64_t>(n_in, (int64_t)kNumSMs * 32);
                 k_row_counts<<<(unsigned)blocks, 256, 0, st>>>(d_col, d_rowptr, k, n_in, og_to_new.p, map_of[(size_t)d],
-                                                              rc_to[(size_t)d].p, err.p);
+                                                              rc_to[(size_t)d], err.p);
                 DN_LAUNCH_CHECK();
                 DN_COUNT_LAUNCH(1);
             }
-            DN_TRY(scan_exclusive<int32_t>(rc_to[(size_t)d].p, off_to[(size_t)d].p, n_in + 1, st));
-            DN_TRY(read_small(e, off_to[(size_t)d].p + n_in, sizeof(int64_t), &send_count[(size_t)d]));
+            DN_TRY(scan_exclusive<int32_t>(rc_to[(size_t)d], off_to[(size_t)d], n_in + 1, st));
+        }
+        // entries bound for each engine: the last offset of every destination, one read-back
+        if (e->h_pinned && (size_t)G * sizeof(int64_t) <= 256) {
+            DN_CUDA(cudaMemcpy2DAsync(e->h_pinned, sizeof(int64_t), off_all.p + n_in, sizeof(int64_t) * ((size_t)n_in + 1),
+                                      sizeof(int64_t), (size_t)G, cudaMemcpyDeviceToHost, st));
+            DN_CUDA(cudaStreamSynchronize(st));
+            memcpy(send_count.data(), e->h_pinned, sizeof(int64_t) * (size_t)G);
+        } else {
+            for (int d = 0; d < G; d++)
+                DN_TRY(read_small(e, off_to[(size_t)d] + n_in, sizeof(int64_t), &send_count[(size_t)d]));
         }
         slice_begin[(size_t)G] = n;
         if (slice->row_begin != slice_begin[(size_t)e->comm_rank] ||
@@ -601,13 +620,13 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
         for (int d = 0; d < G; d++) {
             const int64_t cnt_d = slice_begin[(size_t)d + 1] - slice_begin[(size_t)d];
             if (d == e->comm_rank) continue;
-            if (n_in > 0) DN_NCCL(nccl_api().Send(rc_to[(size_t)d].p, (size_t)n_in, ncclInt32, d, e->comm, st));
+            if (n_in > 0) DN_NCCL(nccl_api().Send(rc_to[(size_t)d], (size_t)n_in, ncclInt32, d, e->comm, st));
             if (cnt_d > 0)
                 DN_NCCL(nccl_api().Recv(row_count.p + slice_begin[(size_t)d], (size_t)cnt_d, ncclInt32, d, e->comm, st));
         }
         DN_NCCL(nccl_api().GroupEnd());
         if (n_in > 0)
-            DN_CUDA(cudaMemcpyAsync(row_count.p + slice->row_begin, rc_to[(size_t)e->comm_rank].p, sizeof(int32_t) * (size_t)n_in,
+            DN_CUDA(cudaMemcpyAsync(row_count.p + slice->row_begin, rc_to[(size_t)e->comm_rank], sizeof(int32_t) * (size_t)n_in,
                                     cudaMemcpyDeviceToDevice, st));
     } else if (n > 0) {
         int64_t blocks = std::min<int64_t>(n, (int64_t)kNumSMs * 32);
@@ -760,8 +779,14 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             }
             float* const cv = e->opt_keep_csr ? e->a_vals : canon_v.p;
             int32_t* const cc = e->opt_keep_csr ? e->a_col : canon_c.p;
-            std::vector<DevBuf<float>> sv((size_t)G);
-            std::vector<DevBuf<int32_t>> sc((size_t)G);
+            // one pair of send buffers, the destinations' parts one after the other
+            DevBuf<float> sv_all;
+            DevBuf<int32_t> sc_all;
+            std::vector<int64_t> send_off((size_t)G + 1, 0);
+            for (int d = 0; d < G; d++)
+                send_off[(size_t)d + 1] = send_off[(size_t)d] + (d == e->comm_rank ? 0 : send_count[(size_t)d]);
+            DN_TRY(sv_all.alloc((size_t)std::max<int64_t>(send_off[(size_t)G], 1)));
+            DN_TRY(sc_all.alloc((size_t)std::max<int64_t>(send_off[(size_t)G], 1)));
             std::vector<int64_t> recv_off((size_t)G + 1, 0);
             for (int d = 0; d <= G; d++)
                 DN_TRY(read_small(e, e->a_rowptr + slice_begin[(size_t)d], sizeof(int64_t), &recv_off[(size_t)d]));
@@ -771,16 +796,14 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
                 float* ov = self ? cv + recv_off[(size_t)d] : nullptr;
                 int32_t* oc = self ? cc + recv_off[(size_t)d] : nullptr;
                 if (!self) {
-                    DN_TRY(sv[(size_t)d].alloc((size_t)std::max<int64_t>(send_count[(size_t)d], 1)));
-                    DN_TRY(sc[(size_t)d].alloc((size_t)std::max<int64_t>(send_count[(size_t)d], 1)));
-                    ov = sv[(size_t)d].p;
-                    oc = sc[(size_t)d].p;
+                    ov = sv_all.p + send_off[(size_t)d];
+                    oc = sc_all.p + send_off[(size_t)d];
                 } else if (send_count[(size_t)d] != recv_off[(size_t)d + 1] - recv_off[(size_t)d]) {
                     return fail(DNPEFF_ERR_INVALID, "internal: row-slice bookkeeping out of step");
                 }
                 if (n_in > 0) {
                     k_extract_shard<<<(unsigned)std::min<int64_t>(n_in, (int64_t)kNumSMs * 32), 256, 0, st>>>(
-                        d_vals, d_col, d_rowptr, k, 0, n_in, d_norms, og_to_new.p, map_of[(size_t)d], off_to[(size_t)d].p,
+                        d_vals, d_col, d_rowptr, k, 0, n_in, d_norms, og_to_new.p, map_of[(size_t)d], off_to[(size_t)d],
                         ov, oc);
                     DN_LAUNCH_CHECK();
                     DN_COUNT_LAUNCH(1);
@@ -790,8 +813,8 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             for (int d = 0; d < G; d++) {
                 if (d == e->comm_rank) continue;
                 if (send_count[(size_t)d] > 0) {
-                    DN_NCCL(nccl_api().Send(sv[(size_t)d].p, (size_t)send_count[(size_t)d], ncclFloat, d, e->comm, st));
-                    DN_NCCL(nccl_api().Send(sc[(size_t)d].p, (size_t)send_count[(size_t)d], ncclInt32, d, e->comm, st));
+                    DN_NCCL(nccl_api().Send(sv_all.p + send_off[(size_t)d], (size_t)send_count[(size_t)d], ncclFloat, d, e->comm, st));
+                    DN_NCCL(nccl_api().Send(sc_all.p + send_off[(size_t)d], (size_t)send_count[(size_t)d], ncclInt32, d, e->comm, st));
                 }
                 const int64_t cnt = recv_off[(size_t)d + 1] - recv_off[(size_t)d];
                 if (cnt > 0) {

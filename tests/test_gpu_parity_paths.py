@@ -218,6 +218,32 @@ def test_host_generator_twin_matches_device_generator(torch_cuda):
         assert np.allclose(norms.cpu().numpy(), hn, rtol=2e-6)
 
 
+def test_streamed_file_loader_matches_array_loader(torch_cuda, tmp_path):
+    """dnpeff_load_pef_hdf5 reads the engine's rows in 64 MB chunks through two pinned
+    staging buffers; a file of 2 600 x 16 384 values (170 MB per dataset) takes three
+    chunks, so both buffers are reused.  The loaded matrix must equal, bit for bit, the
+    one dnpeff_set_csr builds from the same arrays; the leading-hyperslab arguments
+    (--n_examples, --n_fisher_values) are covered too."""
+    import ctypes as C
+    from npeff_ref_b200 import MuNmfParams
+    from npeff_ref_b200._lib import lib, check
+    n, m, k = 2600, 300000, 16384
+    vals, idx, norms = O.synth_pef_hashed(n, m, k, seed=12)
+    path = str(tmp_path / "pef.h5")
+    check(lib().dnpeff_write_pef_hdf5(path.encode(), n, k, C.c_void_p(vals.ctypes.data), C.c_void_p(idx.ctypes.data),
+                                      C.c_void_p(norms.ctypes.data), m))
+    for (ne, nk) in [(0, 0), (1500, 9000)]:
+        rows, cols = (ne or n), (nk or k)
+        with _engine(MuNmfParams(rank=8), [("keep_canonical_csr", 1)]) as a, \
+                _engine(MuNmfParams(rank=8), [("keep_canonical_csr", 1)]) as b:
+            check(lib().dnpeff_load_pef_hdf5(a._h, path.encode(), ne, nk, 2))
+            b.set_csr(rows, m, np.ascontiguousarray(vals[:rows, :cols]), np.ascontiguousarray(idx[:rows, :cols]),
+                      None, cols, norms[:rows], 2)
+            assert a.shape == b.shape and np.array_equal(a.new_to_og(), b.new_to_og())
+            for x, y in zip(a.export_shard_csr(), b.export_shard_csr()):
+                assert np.array_equal(x, y)
+
+
 def test_device_generator_row_ranges_are_slices_of_the_matrix(torch_cuda):
     """dnpeff_synth_pef_device_rows: a row's content depends on its index and the seed
     only, so a rank of a row-split job generates exactly its slice of the matrix."""
