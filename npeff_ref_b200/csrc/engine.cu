@@ -616,15 +616,18 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
             n_in != slice_begin[(size_t)e->comm_rank + 1] - slice_begin[(size_t)e->comm_rank])
             return fail(DNPEFF_ERR_INVALID, "row slice of engine %d must be rows [%lld, %lld)", e->comm_rank,
                         (long long)slice_begin[(size_t)e->comm_rank], (long long)slice_begin[(size_t)e->comm_rank + 1]);
+        int gs = DNPEFF_OK;
         DN_NCCL(nccl_api().GroupStart());
         for (int d = 0; d < G; d++) {
             const int64_t cnt_d = slice_begin[(size_t)d + 1] - slice_begin[(size_t)d];
             if (d == e->comm_rank) continue;
-            if (n_in > 0) DN_NCCL(nccl_api().Send(rc_to[(size_t)d], (size_t)n_in, ncclInt32, d, e->comm, st));
+            if (n_in > 0) DN_NCCL_IN_GROUP(gs, nccl_api().Send(rc_to[(size_t)d], (size_t)n_in, ncclInt32, d, e->comm, st));
             if (cnt_d > 0)
-                DN_NCCL(nccl_api().Recv(row_count.p + slice_begin[(size_t)d], (size_t)cnt_d, ncclInt32, d, e->comm, st));
+                DN_NCCL_IN_GROUP(gs, nccl_api().Recv(row_count.p + slice_begin[(size_t)d], (size_t)cnt_d, ncclInt32, d,
+                                                     e->comm, st));
         }
         DN_NCCL(nccl_api().GroupEnd());
+        DN_TRY(gs);
         if (n_in > 0)
             DN_CUDA(cudaMemcpyAsync(row_count.p + slice->row_begin, rc_to[(size_t)e->comm_rank], sizeof(int32_t) * (size_t)n_in,
                                     cudaMemcpyDeviceToDevice, st));
@@ -809,20 +812,24 @@ int load_device(dnpeff_engine* e, int64_t n, int64_t m_full, int64_t k, const in
                     DN_COUNT_LAUNCH(1);
                 }
             }
+            int gs = DNPEFF_OK;
             DN_NCCL(nccl_api().GroupStart());
             for (int d = 0; d < G; d++) {
                 if (d == e->comm_rank) continue;
                 if (send_count[(size_t)d] > 0) {
-                    DN_NCCL(nccl_api().Send(sv_all.p + send_off[(size_t)d], (size_t)send_count[(size_t)d], ncclFloat, d, e->comm, st));
-                    DN_NCCL(nccl_api().Send(sc_all.p + send_off[(size_t)d], (size_t)send_count[(size_t)d], ncclInt32, d, e->comm, st));
+                    DN_NCCL_IN_GROUP(gs, nccl_api().Send(sv_all.p + send_off[(size_t)d], (size_t)send_count[(size_t)d],
+                                                         ncclFloat, d, e->comm, st));
+                    DN_NCCL_IN_GROUP(gs, nccl_api().Send(sc_all.p + send_off[(size_t)d], (size_t)send_count[(size_t)d],
+                                                         ncclInt32, d, e->comm, st));
                 }
                 const int64_t cnt = recv_off[(size_t)d + 1] - recv_off[(size_t)d];
                 if (cnt > 0) {
-                    DN_NCCL(nccl_api().Recv(cv + recv_off[(size_t)d], (size_t)cnt, ncclFloat, d, e->comm, st));
-                    DN_NCCL(nccl_api().Recv(cc + recv_off[(size_t)d], (size_t)cnt, ncclInt32, d, e->comm, st));
+                    DN_NCCL_IN_GROUP(gs, nccl_api().Recv(cv + recv_off[(size_t)d], (size_t)cnt, ncclFloat, d, e->comm, st));
+                    DN_NCCL_IN_GROUP(gs, nccl_api().Recv(cc + recv_off[(size_t)d], (size_t)cnt, ncclInt32, d, e->comm, st));
                 }
             }
             DN_NCCL(nccl_api().GroupEnd());
+            DN_TRY(gs);
             DN_CUDA(cudaStreamSynchronize(st));  // the send buffers are released here
             trace.mark("row slices exchanged");
         }
@@ -1856,13 +1863,16 @@ int dnpeff_comm_init(dnpeff_engine* e, const void* id128, int comm_rank, int com
     DevBuf<float> one;
     DN_TRY(one.alloc_zero(32 + 2 * kWarm * (size_t)comm_size, e->st));
     DN_NCCL(nccl_api().AllReduce(one.p, one.p, 32, ncclFloat, ncclSum, e->comm, e->st));
+    int gs = DNPEFF_OK;
     DN_NCCL(nccl_api().GroupStart());
     for (int d = 0; d < comm_size; d++) {
         if (d == comm_rank) continue;
-        DN_NCCL(nccl_api().Send(one.p + 32 + kWarm * (size_t)d, kWarm, ncclFloat, d, e->comm, e->st));
-        DN_NCCL(nccl_api().Recv(one.p + 32 + kWarm * (size_t)(comm_size + d), kWarm, ncclFloat, d, e->comm, e->st));
+        DN_NCCL_IN_GROUP(gs, nccl_api().Send(one.p + 32 + kWarm * (size_t)d, kWarm, ncclFloat, d, e->comm, e->st));
+        DN_NCCL_IN_GROUP(gs, nccl_api().Recv(one.p + 32 + kWarm * (size_t)(comm_size + d), kWarm, ncclFloat, d, e->comm,
+                                             e->st));
     }
     DN_NCCL(nccl_api().GroupEnd());
+    DN_TRY(gs);
     DN_CUDA(cudaStreamSynchronize(e->st));
     return DNPEFF_OK;
 }

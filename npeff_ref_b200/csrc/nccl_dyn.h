@@ -67,4 +67,17 @@ inline int nccl_load() {
                                   #call, ::dnpeff::nccl_api().GetErrorString(r_));     \
     } while (0)
 
+// Inside an ncclGroupStart / ncclGroupEnd section a failed call must not return before
+// the group is closed: it records the failure in `status` instead and the later calls
+// of the section are skipped.
+#define DN_NCCL_IN_GROUP(status, call)                                                        \
+    do {                                                                                      \
+        if ((status) == DNPEFF_OK) {                                                          \
+            ncclResult_t r_ = (call);                                                         \
+            if (r_ != ncclSuccess)                                                            \
+                (status) = ::dnpeff::fail(DNPEFF_ERR_NCCL, "%s:%d: %s -> %s", __FILE__, __LINE__, \
+                                          #call, ::dnpeff::nccl_api().GetErrorString(r_));    \
+        }                                                                                     \
+    } while (0)
+
 }  // namespace dnpeff
