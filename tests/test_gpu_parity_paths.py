@@ -298,3 +298,50 @@ def test_bounded_wait_runs_out_and_engine_recovers(torch_cuda):
         eng.step_w()
         W1 = eng.load_w_to_host()
         assert rel_fro(W1, O.step_w(v, c, rp, mk, W0, H0, eps)) < 2e-6
+
+
+# ---------------------------------------------------------------------------
+_NO_TC_SCRIPT = r"""
+import sys, numpy as np
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from npeff_ref_b200 import MuNmf, MuNmfParams
+from helpers import make_problem
+n, m, k, r = 300, 9000, 1500, 128
+vals, idx, norms = make_problem(n, m, k, seed=428)
+with MuNmf(MuNmfParams(rank=r, eps=1e-12, seed=0, init_scale=float(sys.argv[3]))) as eng:
+    eng.set_csr(n, m, vals, idx, None, k, norms, 1)
+    layout = eng.layout()
+    eng.init_factors()
+    eng.run(20, log_every=0)
+    np.savez(sys.argv[2], W=eng.load_w_to_host(), H=eng.load_h_to_host(), loss=eng.compute_uncached_loss(),
+             tile_rows=layout[3])
+"""
+
+
+def test_cuda_core_path_at_a_tensor_core_rank(torch_cuda, tmp_path):
+    """DNPEFF_NO_TC=1 keeps every contraction on the CUDA-core kernels and the popular
+    columns on the shared-memory tiled sparse kernel (the path other ranks take, and the
+    A/B comparison for the tensor-core kernels).  At rank 128 it must match the oracle
+    like the tensor-core path does."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    n, m, k, r, iters = 300, 9000, 1500, 128, 20
+    vals, idx, norms = make_problem(n, m, k, seed=428)
+    v, c, rp, n2o = oracle_preprocess(vals, idx, norms, m)
+    mk = len(n2o)
+    scale = baseline_scale(v, n, mk, r)
+    W0, H0 = O.init_factors(n, mk, r, 0, scale)
+    Wo, Ho, ls = O.run(v, c, rp, mk, W0, H0, iters, 1e-12, acc64=True, losses=True)
+    outs = {}
+    for name, env in (("tc", {}), ("no_tc", {"DNPEFF_NO_TC": "1"})):
+        out = str(tmp_path / (name + ".npz"))
+        res = subprocess.run([sys.executable, "-c", _NO_TC_SCRIPT, root, out, repr(scale)],
+                             env=dict(os.environ, **env), capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, res.stderr[-2000:]
+        outs[name] = np.load(out)
+    assert int(outs["tc"]["tile_rows"]) == 0 and int(outs["no_tc"]["tile_rows"]) > 0   # dense block / tiled sparse kernel
+    for name in outs:
+        assert rel_fro(outs[name]["W"], Wo) < 1e-4 and rel_fro(outs[name]["H"], Ho) < 1e-4, name
+        assert abs(float(outs[name]["loss"]) - ls[-1]) < 1e-5 * ls[-1], name
