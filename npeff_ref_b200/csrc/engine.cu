@@ -348,7 +348,9 @@ size_t gram_any_scratch(int64_t rows, int r) {
 // cannot update X in place and then writes its result over Num before copying it back).
 int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int r, float eps,
                   float* tc_scratch, int* err, cudaStream_t st, bool num_is_scratch = false,
-                  float* out_buf = nullptr) {
+                  float* out_buf = nullptr, uint32_t wait_limit = kTiledSpinLimit) {
+    if (tensor_cores_enabled() && mu_update_ws_ok(r))
+        return mu_update_ws_launch(X, Num, G, rows, r, eps, tc_scratch, err, st, wait_limit);
     if (tensor_cores_enabled() && mu_update_tc_ok(r))
         return mu_update_tc_launch(X, Num, G, rows, r, eps, tc_scratch, err, st);
     if (tensor_cores_enabled() && mu_update_wide_ok(r) && rows > 0) {
@@ -1170,7 +1172,7 @@ int step_w(dnpeff_engine* e) {
     }
     ScopedTimer t(e, 3);
     return mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
-                         spare);
+                         spare, e->opt_wait_limit);
 }
 
 int step_h(dnpeff_engine* e) {
@@ -1186,7 +1188,8 @@ int step_h(dnpeff_engine* e) {
         DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st, e->opt_wait_limit));
     }
     ScopedTimer t(e, 3);
-    return mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st, true);
+    return mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st, true, nullptr,
+                         e->opt_wait_limit);
 }
 
 int global_a_sq(dnpeff_engine* e, double* out) {
@@ -1949,7 +1952,7 @@ int dnpeff_fit_w_only(dnpeff_engine* e, int32_t iters, double* loss) {
     for (int it = 0; it < iters; it++) {
         ScopedTimer t(e, 3);
         DN_TRY(mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
-                             e->w_spare));
+                             e->w_spare, e->opt_wait_limit));
     }
     if (loss) DN_TRY(loss_from_current(e, false, loss));
     return DNPEFF_OK;
