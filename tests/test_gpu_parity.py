@@ -125,6 +125,33 @@ def test_op_mu_update_matches_oracle(torch_cuda, rows, r):
     assert np.allclose(got, want, rtol=3e-6, atol=0), np.abs(got / want - 1).max()
 
 
+@pytest.mark.parametrize("rows,r", [(1000, 128), (20000, 64), (300, 32), (257, 256)])
+def test_op_mu_update_zero_and_tiny_numerators(torch_cuda, rows, r):
+    """Numerators that are exactly zero or below 2^-100, and rows of X that are zero (their
+    denominators are then eps alone): the tensor-core update kernels of ranks 64 and 128
+    leave their branch-free division for the IEEE one on such batches; every kernel must
+    still give the reference's x * (num / (den + eps))."""
+    from npeff_ref_b200._lib import lib, check
+    torch = torch_cuda
+    rng = np.random.default_rng(rows + r)
+    X = rng.random((rows, r), dtype=np.float32)
+    Num = rng.random((rows, r), dtype=np.float32)
+    Num[rng.random((rows, r)) < 0.05] = 0.0
+    Num[rng.random((rows, r)) < 0.05] = np.float32(3e-36)
+    X[::7] = 0.0
+    B = rng.random((r + 3, r), dtype=np.float32)
+    G = (B.T @ B).astype(np.float32)
+    want = O.mu_update(X, Num, G, 1e-8, acc64=True)
+    dX, dN, dG = _dev(torch, X), _dev(torch, Num), _dev(torch, G)
+    st = torch.cuda.current_stream().cuda_stream
+    check(lib().dnpeff_op_mu_update(dX.data_ptr(), dN.data_ptr(), dG.data_ptr(), rows, r, 1e-8, st))
+    torch.cuda.synchronize()
+    got = dX.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.array_equal(got == 0, want == 0)
+    assert np.allclose(got, want, rtol=3e-6, atol=1e-44), np.abs(got - want).max()
+
+
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("min_count", [1, 2, 3])
 @pytest.mark.parametrize("n_shards", [1, 3])
