@@ -106,7 +106,8 @@ def test_op_gram_matches_oracle(torch_cuda, rows, r):
 
 @pytest.mark.parametrize("rows,r", [(1, 4), (513, 32), (300, 64), (1000, 48), (4099, 128),
                                     (700, 256), (200, 512), (3000, 384), (50, 5), (64, 516),
-                                    (40001, 128), (60000, 64)])   # several tiles per block
+                                    (40001, 128), (60000, 64),    # several tiles per block
+                                    (1, 128), (100, 64), (127, 128), (129, 64)])  # fewer rows than a tile
 def test_op_mu_update_matches_oracle(torch_cuda, rows, r):
     from npeff_ref_b200._lib import lib, check
     torch = torch_cuda
