@@ -170,7 +170,7 @@ struct dnpeff_engine {
     int32_t* c_row = nullptr;
     int64_t* c_colptr = nullptr;
     int64_t c_base = 0;
-    float* w_spare = nullptr;  // n x r, wide ranks only: where a W update is written before it replaces W
+    float* w_spare = nullptr;  // n x r, wide ranks only: a W update is written here, then W and w_spare change places
     int32_t* new_to_og = nullptr;
 
     // Internal column order: [n_hot popular columns][the rest], each in local-id
@@ -344,19 +344,21 @@ size_t gram_any_scratch(int64_t rows, int r) {
 }
 
 // tc_scratch: 2*r*r floats.
-// num_is_scratch: the caller does not need Num after the call (the wide-rank kernel
-// cannot update X in place and then writes its result over Num before copying it back).
+// The wide-rank kernels cannot update X in place: their result goes to Num when the caller
+// is done with it (num_is_scratch), else to the caller's spare buffer of rows * r floats
+// (out_buf), else to a temporary.  With `moved` given, the result stays there and *moved
+// tells the caller to exchange its two buffers; without it, one device copy brings the
+// result back to X.
 int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int r, float eps,
                   float* tc_scratch, int* err, cudaStream_t st, bool num_is_scratch = false,
-                  float* out_buf = nullptr, uint32_t wait_limit = kTiledSpinLimit) {
+                  float* out_buf = nullptr, uint32_t wait_limit = kTiledSpinLimit, bool* moved = nullptr) {
+    if (moved) *moved = false;
     if (tensor_cores_enabled() && mu_update_ws_ok(r))
         return mu_update_ws_launch(X, Num, G, rows, r, eps, tc_scratch, err, st, wait_limit);
     if (tensor_cores_enabled() && mu_update_tc_ok(r))
         return mu_update_tc_launch(X, Num, G, rows, r, eps, tc_scratch, err, st);
     if (tensor_cores_enabled() && mu_update_wide_ok(r) && rows > 0) {
         DevBuf<float> tmp;
-        // the result goes to Num when the caller is done with it, else to the caller's
-        // spare buffer of rows * r floats, else to a temporary
         float* out = num_is_scratch ? const_cast<float*>(Num) : out_buf;
         if (!out) {
             DN_TRY(tmp.alloc((size_t)(rows * r)));
@@ -366,6 +368,10 @@ int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int 
             DN_TRY(mu_update_wide2_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
         else
             DN_TRY(mu_update_wide_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
+        if (moved && !tmp.p) {
+            *moved = true;
+            return DNPEFF_OK;
+        }
         DN_CUDA(cudaMemcpyAsync(X, out, sizeof(float) * (size_t)(rows * r), cudaMemcpyDeviceToDevice, st));
         if (tmp.p) DN_CUDA(cudaStreamSynchronize(st));  // tmp is released on return
         return DNPEFF_OK;
@@ -1158,21 +1164,16 @@ int compute_ah_hh(dnpeff_engine* e) {
 int step_w(dnpeff_engine* e) {
     const int r = e->p.rank;
     DN_TRY(compute_ah_hh(e));
-    // Wide ranks write the updated W beside the old one.  The buffer of W^T*A (ms x r)
-    // is idle during a W update and serves when it exists and is large enough;
-    // otherwise the engine keeps a spare n x r buffer (allocated once).
-    float* spare = nullptr;
-    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0) {
-        if (e->WA && e->ms >= e->n) {
-            spare = e->WA;
-        } else {
-            if (!e->w_spare) DN_CUDA(cudaMalloc((void**)&e->w_spare, sizeof(float) * (size_t)(e->n * r)));
-            spare = e->w_spare;
-        }
-    }
+    // Wide ranks write the updated W beside the old one, into the engine's spare n x r
+    // buffer (allocated once), and the two buffers change places.
+    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0 && !e->w_spare)
+        DN_CUDA(cudaMalloc((void**)&e->w_spare, sizeof(float) * (size_t)(e->n * r)));
     ScopedTimer t(e, 3);
-    return mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
-                         spare, e->opt_wait_limit);
+    bool moved = false;
+    DN_TRY(mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
+                         e->w_spare, e->opt_wait_limit, &moved));
+    if (moved) std::swap(e->W, e->w_spare);
+    return DNPEFF_OK;
 }
 
 int step_h(dnpeff_engine* e) {
@@ -1188,8 +1189,12 @@ int step_h(dnpeff_engine* e) {
         DN_TRY(gram_any(e->W, e->n, r, e->WW, e->gram_scratch, e->d_err, e->st, e->opt_wait_limit));
     }
     ScopedTimer t(e, 3);
-    return mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st, true, nullptr,
-                         e->opt_wait_limit);
+    // wide ranks: the new H is written over W^T*A (not used again), and the buffers change places
+    bool moved = false;
+    DN_TRY(mu_update_any(e->H, e->WA, e->WW, e->ms, r, e->p.eps, e->tc_scratch, e->d_err, e->st, true, nullptr,
+                         e->opt_wait_limit, &moved));
+    if (moved) std::swap(e->H, e->WA);
+    return DNPEFF_OK;
 }
 
 int global_a_sq(dnpeff_engine* e, double* out) {
@@ -1951,8 +1956,10 @@ int dnpeff_fit_w_only(dnpeff_engine* e, int32_t iters, double* loss) {
         DN_CUDA(cudaMalloc((void**)&e->w_spare, sizeof(float) * (size_t)(e->n * r)));
     for (int it = 0; it < iters; it++) {
         ScopedTimer t(e, 3);
+        bool moved = false;
         DN_TRY(mu_update_any(e->W, e->AHG, e->AHG + e->n * r, e->n, r, e->p.eps, e->tc_scratch, e->d_err, e->st, false,
-                             e->w_spare, e->opt_wait_limit));
+                             e->w_spare, e->opt_wait_limit, &moved));
+        if (moved) std::swap(e->W, e->w_spare);
     }
     if (loss) DN_TRY(loss_from_current(e, false, loss));
     return DNPEFF_OK;
