@@ -354,20 +354,17 @@ int mu_update_any(float* X, const float* Num, const float* G, int64_t rows, int 
                   float* out_buf = nullptr, uint32_t wait_limit = kTiledSpinLimit, bool* moved = nullptr) {
     if (moved) *moved = false;
     if (tensor_cores_enabled() && mu_update_ws_ok(r))
-        return mu_update_ws_launch(X, Num, G, rows, r, eps, tc_scratch, err, st, wait_limit);
+        return mu_update_ws_launch(X, Num, X, G, rows, r, eps, tc_scratch, err, st, wait_limit);
     if (tensor_cores_enabled() && mu_update_tc_ok(r))
         return mu_update_tc_launch(X, Num, G, rows, r, eps, tc_scratch, err, st);
-    if (tensor_cores_enabled() && mu_update_wide_ok(r) && rows > 0) {
+    if (tensor_cores_enabled() && mu_update_ws_wide_ok(r) && rows > 0) {
         DevBuf<float> tmp;
         float* out = num_is_scratch ? const_cast<float*>(Num) : out_buf;
         if (!out) {
             DN_TRY(tmp.alloc((size_t)(rows * r)));
             out = tmp.p;
         }
-        if (mu_update_wide2_ok(r))
-            DN_TRY(mu_update_wide2_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
-        else
-            DN_TRY(mu_update_wide_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st));
+        DN_TRY(mu_update_ws_launch(X, Num, out, G, rows, r, eps, tc_scratch, err, st, wait_limit));
         if (moved && !tmp.p) {
             *moved = true;
             return DNPEFF_OK;
@@ -1166,7 +1163,7 @@ int step_w(dnpeff_engine* e) {
     DN_TRY(compute_ah_hh(e));
     // Wide ranks write the updated W beside the old one, into the engine's spare n x r
     // buffer (allocated once), and the two buffers change places.
-    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0 && !e->w_spare)
+    if (tensor_cores_enabled() && mu_update_ws_wide_ok(r) && e->n > 0 && !e->w_spare)
         DN_CUDA(cudaMalloc((void**)&e->w_spare, sizeof(float) * (size_t)(e->n * r)));
     ScopedTimer t(e, 3);
     bool moved = false;
@@ -1952,7 +1949,7 @@ int dnpeff_fit_w_only(dnpeff_engine* e, int32_t iters, double* loss) {
     const int r = e->p.rank;
     DN_TRY(compute_ah_hh(e));
     // wide ranks write the updated W beside the old one: the engine's spare n x r buffer
-    if (tensor_cores_enabled() && mu_update_wide_ok(r) && e->n > 0 && !e->w_spare)
+    if (tensor_cores_enabled() && mu_update_ws_wide_ok(r) && e->n > 0 && !e->w_spare)
         DN_CUDA(cudaMalloc((void**)&e->w_spare, sizeof(float) * (size_t)(e->n * r)));
     for (int it = 0; it < iters; it++) {
         ScopedTimer t(e, 3);
