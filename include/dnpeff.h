@@ -94,10 +94,10 @@ int dnpeff_destroy(dnpeff_engine* eng);
  *   "keep_canonical_csr" 1: keep the shard's CSR in input order after the loader has
  *                       built its own layout (needed by dnpeff_export_shard_csr;
  *                       costs 8 bytes per stored entry; default 0)
- *   "wait_limit"        polls after which a wait between the roles of the
- *                       warp-specialised tensor-core kernel gives up (default 2^24);
- *                       the kernel then leaves cleanly and the next call that reads the
- *                       engine's status returns DNPEFF_ERR_CUDA
+ *   "wait_limit"        polls after which a wait between the roles of a
+ *                       warp-specialised tensor-core kernel (dense block, Gram, update)
+ *                       gives up (default 2^24); the kernel then leaves cleanly and the
+ *                       next call that reads the engine's status returns DNPEFF_ERR_CUDA
  * Unknown names fail with DNPEFF_ERR_INVALID. */
 int dnpeff_set_option(dnpeff_engine* eng, const char* name, int64_t value);
 
